@@ -4,9 +4,10 @@ from .mekazen import MekazenConfig
 from .qwen3 import ConfigError, Qwen3Config
 from .registry import (ModelFamily, family_by_kind, parse_config, read_config, register,
                        resolve, unregister)
+from .sadosun import SadosunConfig
 from .zitezen import ZitezenConfig
 from .spec import CacheNeed, LayerRun, LayerSpec, ModelSpec, PartSpec
 
-__all__ = ["ConfigError", "MekazenConfig", "Qwen3Config", "ZitezenConfig", "ModelFamily", "family_by_kind", "parse_config",
+__all__ = ["ConfigError", "MekazenConfig", "Qwen3Config", "ZitezenConfig", "SadosunConfig", "ModelFamily", "family_by_kind", "parse_config",
            "read_config", "register", "resolve", "unregister", "CacheNeed", "LayerRun",
            "LayerSpec", "ModelSpec", "PartSpec"]

@@ -17,6 +17,7 @@ from typing import Any, Dict, Mapping, Optional, Type
 
 from .mekazen import MekazenConfig
 from .qwen3 import ConfigError, Qwen3Config
+from .sadosun import SadosunConfig
 from .zitezen import ZitezenConfig
 
 
@@ -132,3 +133,6 @@ register(MEKAZEN)
 ZITEZEN = ModelFamily(architecture=ZitezenConfig.ARCHITECTURE, model_type=ZitezenConfig.MODEL_TYPE,
                       kind="zitezen", config_class=ZitezenConfig)
 register(ZITEZEN)
+SADOSUN = ModelFamily(architecture=SadosunConfig.ARCHITECTURE, model_type=SadosunConfig.MODEL_TYPE,
+                      kind="sadosun", config_class=SadosunConfig)
+register(SADOSUN)

@@ -15,11 +15,11 @@ bool chained_launches() { return g_chained_launches; }
 unsigned chained_block_limit() { return g_chained_block_limit; }
 unsigned long long chained_byte_limit() { return g_chained_byte_limit; }
 
-// out[t, :] = table[ids[t], :] as float32. A bad id sets the status word and
-// writes zeros.
+// out[t, :] = table[ids[t], :] * scale as float32. A bad id sets the status
+// word and writes zeros.
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
-                             const int* __restrict__ ids, int hidden, int vocab, int* status) {
+                             const int* __restrict__ ids, int hidden, int vocab, float scale, int* status) {
   chain_release();
   chain_wait();
   const int t = blockIdx.x;
@@ -28,7 +28,7 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
   if (!ok && threadIdx.x == 0) atomicOr(status, kStatusBadTokenId);
   const T* row = table + static_cast<size_t>(ok ? id : 0) * hidden;
   float* dst = out + static_cast<size_t>(t) * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? to_float(row[i]) : 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? to_float(row[i]) * scale : 0.0f;
 }
 
 // y[r, :] = x[src(r), :] * rsqrt(mean(x^2) + eps) * w, one block per row.
@@ -229,14 +229,14 @@ static int norm_threads(int size) {
 using namespace mxb;
 
 MXB_API int mxb_embed(float* out, const void* table, int table_dtype, const int* ids, int tokens,
-                      int hidden, int vocab, int* status, cudaStream_t stream) {
+                      int hidden, int vocab, float scale, int* status, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int threads = hidden >= 256 ? 256 : 128;
   if (table_dtype == kF32)
     return static_cast<int>(launch_chained(embed_kernel<float>, dim3(tokens), dim3(threads), 0, stream, out,
-                                           static_cast<const float*>(table), ids, hidden, vocab, status));
+                                           static_cast<const float*>(table), ids, hidden, vocab, scale, status));
   return static_cast<int>(launch_chained(embed_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, out,
-                                         static_cast<const __nv_bfloat16*>(table), ids, hidden, vocab, status));
+                                         static_cast<const __nv_bfloat16*>(table), ids, hidden, vocab, scale, status));
 }
 
 MXB_API int mxb_rmsnorm(void* y, int y_dtype, const void* x, int x_dtype, const float* w,

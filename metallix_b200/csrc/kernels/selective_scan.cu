@@ -1,0 +1,132 @@
+// The selective state-space recurrence (Mamba's scan) over the packed tokens
+// of a step, with the state kept per request.
+//
+// Per channel c and state n, with a step size d_t[c] = softplus(p_t[c] + b[c])
+// that depends on the token:
+//
+//   S[c, n] <- exp(d_t[c] A[c, n]) S[c, n] + d_t[c] x_t[c] B_t[n]
+//   y_t[c]  =  sum_n S[c, n] C_t[n] + D[c] x_t[c]
+//   out_t[c] = y_t[c] * silu(z_t[c])
+//
+// Step sizes, decays, exponentials, the state and the sums are float32 in
+// both precisions; x, B, C and z arrive in the compute type. Four lanes share
+// a channel, each owning every fourth state in registers; a request row's
+// tokens are walked in order, so what a position gets does not depend on how
+// the sequence was cut into steps. `state` is [slots, channels, states]
+// float32; a row of length 0 touches no slot.
+#include "common.cuh"
+
+namespace mxb {
+
+constexpr int kScanLanes = 4;          // lanes that share a channel
+constexpr int kScanThreads = 128;      // 32 channels a block
+
+__device__ __forceinline__ float softplus_of(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+template <typename T, int PER>
+__global__ void __launch_bounds__(kScanThreads)
+selective_scan_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ step, long long ld_step,
+                      const float* __restrict__ step_bias, const float* __restrict__ a, const T* __restrict__ b,
+                      const T* __restrict__ c, long long ldbc, const float* __restrict__ d, const T* __restrict__ z,
+                      long long ldz, float* __restrict__ state, const int* __restrict__ row_start,
+                      const int* __restrict__ row_length, const int* __restrict__ request_slots,
+                      T* __restrict__ out, int channels, int states, int num_slots, int* status) {
+  const int row = blockIdx.y;
+  const int n = row_length[row];
+  if (n <= 0) return;
+  const int slot = request_slots[row];
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, kStatusBadSlot);
+    return;
+  }
+  const int lane = threadIdx.x & (kScanLanes - 1);
+  const int ch = blockIdx.x * (kScanThreads / kScanLanes) + (threadIdx.x / kScanLanes);
+  const bool live = ch < channels;
+  const int cc = live ? ch : channels - 1;      // idle lanes of the last block shadow a real channel and write nothing
+  const int start = row_start[row];
+  float* held = state + (static_cast<size_t>(slot) * channels + cc) * states;
+  float s[PER], decay[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int k = lane + kScanLanes * j;
+    s[j] = k < states ? held[k] : 0.0f;
+    decay[j] = k < states ? a[static_cast<size_t>(cc) * states + k] : 0.0f;
+  }
+  const float bias = step_bias[cc], skip = d[cc];
+  for (int i = 0; i < n; ++i) {
+    const size_t t = static_cast<size_t>(start + i);
+    const float dt = softplus_of(step[t * ld_step + cc] + bias);
+    const float xv = to_float(x[t * ldx + cc]);
+    const float dx = dt * xv;
+    const T* bt = b + t * ldbc;
+    const T* ct = c + t * ldbc;
+    float y = 0.0f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int k = lane + kScanLanes * j;
+      if (k < states) {
+        s[j] = fmaf(expf(dt * decay[j]), s[j], dx * to_float(bt[k]));
+        y = fmaf(s[j], to_float(ct[k]), y);
+      }
+    }
+    y += __shfl_xor_sync(0xffffffffu, y, 1);
+    y += __shfl_xor_sync(0xffffffffu, y, 2);
+    if (lane == 0 && live) {
+      const float zv = to_float(z[t * ldz + cc]);
+      out[t * channels + cc] = from_float<T>(fmaf(skip, xv, y) * (zv / (1.0f + expf(-zv))));
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int k = lane + kScanLanes * j;
+      if (k < states) held[k] = s[j];
+    }
+  }
+}
+
+template <typename T, int PER>
+static int launch_scan(const void* x, long long ldx, const float* step, long long ld_step, const float* step_bias,
+                       const float* a, const void* b, const void* c, long long ldbc, const float* d, const void* z,
+                       long long ldz, float* state, const int* row_start, const int* row_length,
+                       const int* request_slots, void* out, int rows, int channels, int states, int num_slots,
+                       int* status, cudaStream_t stream) {
+  dim3 grid(ceil_div(channels, kScanThreads / kScanLanes), rows);
+  selective_scan_kernel<T, PER><<<grid, kScanThreads, 0, stream>>>(
+      static_cast<const T*>(x), ldx, step, ld_step, step_bias, a, static_cast<const T*>(b), static_cast<const T*>(c),
+      ldbc, d, static_cast<const T*>(z), ldz, state, row_start, row_length, request_slots, static_cast<T*>(out),
+      channels, states, num_slots, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace mxb
+
+using namespace mxb;
+
+// x, z: [tokens, channels] (row strides ldx, ldz); step: float32 [tokens, channels] ahead of its bias and softplus;
+// a: float32 [channels, states] (negative); b, c: [tokens, states] with row stride ldbc; d: [channels];
+// out: [tokens, channels] contiguous. Up to 256 states.
+MXB_API int mxb_selective_scan(const void* x, long long ldx, const float* step, long long ld_step,
+                               const float* step_bias, const float* a, const void* b, const void* c, long long ldbc,
+                               const float* d, const void* z, long long ldz, float* state, const int* row_start,
+                               const int* row_length, const int* request_slots, void* out, int rows, int channels,
+                               int states, int num_slots, int dtype, int* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (channels <= 0 || states <= 0 || states > 64 * kScanLanes) return static_cast<int>(cudaErrorInvalidValue);
+  const int per = ceil_div(states, kScanLanes);
+#define ARGS x, ldx, step, ld_step, step_bias, a, b, c, ldbc, d, z, ldz, state, row_start, row_length, request_slots, \
+             out, rows, channels, states, num_slots, status, stream
+#define DISPATCH(T)                                    \
+  if (per <= 1) return launch_scan<T, 1>(ARGS);        \
+  if (per <= 2) return launch_scan<T, 2>(ARGS);        \
+  if (per <= 4) return launch_scan<T, 4>(ARGS);        \
+  if (per <= 8) return launch_scan<T, 8>(ARGS);        \
+  if (per <= 16) return launch_scan<T, 16>(ARGS);      \
+  if (per <= 32) return launch_scan<T, 32>(ARGS);      \
+  return launch_scan<T, 64>(ARGS);
+  if (dtype == kF32) { DISPATCH(float) }
+  if (dtype == kBF16) { DISPATCH(__nv_bfloat16) }
+#undef DISPATCH
+#undef ARGS
+  return static_cast<int>(cudaErrorInvalidValue);
+}

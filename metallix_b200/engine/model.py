@@ -45,7 +45,8 @@ class DecoderModel:
         needs: List[Optional[CacheNeed]] = [None] * self.spec.num_cache_entries()
         for run in self.order:
             entry = run.cache_entry()
-            need = self.blocks[run.layer].mixer.cache_need()
+            block = self.blocks[run.layer]   # an arrangement that keeps state of its own beside its mixer's says so
+            need = block.cache_need() if hasattr(block, "cache_need") else block.mixer.cache_need()
             if run.write_cache or needs[entry] is None:
                 if needs[entry] is not None and needs[entry].group_key() != need.group_key() \
                         and run.write_cache:
@@ -69,6 +70,7 @@ class DecoderModel:
         ``[tokens, hidden]`` as that layer leaves it (the sums that otherwise
         ride along into the next layer's first kernel are made at once then)."""
         residual = self.embedding.forward(token_ids)
+        ctx.token_ids = token_ids
         streams = self.spec.streams
         if streams:   # several copies of the stream: [tokens, streams, hidden]
             residual = open_streams(residual, streams)

@@ -27,7 +27,7 @@ class KernelError(RuntimeError):
 
 _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 _SIGNATURES = {
-    "mxb_embed": [_P, _P, _I, _P, _I, _I, _I, _P, _P],
+    "mxb_embed": [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P],
     "mxb_rmsnorm": [_P, _I, _P, _I, _P, _P, _I, _I, _F, _P],
     "mxb_add_rmsnorm": [_P, _P, _I, _P, _I, _P, _I, _I, _F, _P],
     "mxb_add_summands_rmsnorm": [_P, _P, _I, _P, _I, _P, _I, _I, _F, _P],
@@ -36,7 +36,16 @@ _SIGNATURES = {
     "mxb_qk_norm_rope_cache": [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P,
                                _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
-                                 _F, _I, _P, _L, _I, _I, _F, _I, _P, _P],
+                                 _F, _I, _P, _L, _I, _I, _F, _I, _I, _F, _P, _P],
+    "mxb_short_conv": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "mxb_selective_scan": [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                           _P, _P],
+    "mxb_route_experts": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "mxb_experts_dense_act": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "mxb_experts_add_identity": [_P, _P, _P, _I, _I, _I, _P],
+    "mxb_experts_routed": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "mxb_add_cast": [_P, _P, _I, _P, _I, _L, _P],
+    "mxb_gelu_gate_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "mxb_stream_mix": [_P, _P, _P, _L, _L, _F, _F, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
     "mxb_weighted_sum": [_P, _P, _P, _L, _L, _F, _F, _I, _I, _I, _P],
     "mxb_mlstm_state_values": [_I, _I, _I],
@@ -245,8 +254,9 @@ def check_status(device) -> None:
 
 
 # ------------------------------------------------------------------ embedding
-def embed(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = table[ids[t]] as float32."""
+def embed(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None,
+          scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[ids[t]] * scale as float32."""
     _check(ids, "ids", (torch.int32,), 1)
     _check(table, "table", tuple(_CODES), 2)
     tokens, (vocab, hidden) = ids.numel(), table.shape
@@ -255,7 +265,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = 
     _check(out, "out", (torch.float32,), 2)
     _need(out.shape == (tokens, hidden), "out has the wrong shape")
     _call("mxb_embed", out.data_ptr(), table.data_ptr(), _CODES[table.dtype], ids.data_ptr(),
-          tokens, hidden, vocab, status_word(ids.device).data_ptr(), _stream())
+          tokens, hidden, vocab, float(scale), status_word(ids.device).data_ptr(), _stream())
     return out
 
 
@@ -451,6 +461,188 @@ def relu_squared(x: torch.Tensor) -> torch.Tensor:
     _check(x, "x", tuple(_CODES))
     out = torch.empty_like(x)
     _call("mxb_relu_squared", out.data_ptr(), x.data_ptr(), x.numel(), _CODES[x.dtype], _stream())
+    return out
+
+
+# ------------------------------------------------ short convolution over time
+def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+               token_request: torch.Tensor, row_start: torch.Tensor, row_length: torch.Tensor,
+               request_slots: torch.Tensor, residual: bool = False, activation: Optional[str] = None) -> torch.Tensor:
+    """A causal convolution over time on each channel of the packed tokens
+    x ``[tokens, channels]`` (rows may be strided): y_t = bias + sum_j
+    w[:, j] x_(t - taps + 1 + j), zeros before a sequence's start; the result is
+    y, or x + y with ``residual``, passed through ``activation`` ("silu").
+    ``weight`` is float32 ``[channels, taps]``, its last column the current
+    token's. ``state`` (float32 ``[slots, taps - 1, channels]``) holds each
+    request's last inputs of earlier steps and is moved on by this step's;
+    request row r owns tokens ``row_start[r] .. + row_length[r]`` and the slot
+    ``request_slots[r]`` (a row of length 0 touches nothing)."""
+    _need(x.is_cuda and x.dtype in _CODES and x.dim() == 2 and x.stride(1) == 1, "x must be [tokens, channels]")
+    tokens, channels = x.shape
+    _check(weight, "weight", (torch.float32,), 2)
+    taps = weight.shape[1]
+    _need(weight.shape[0] == channels and 1 <= taps <= 64, "weight must be [channels, taps]")
+    if bias is not None:
+        _check(bias, "bias", (torch.float32,), 1)
+        _need(bias.numel() == channels, "bias must have one value per channel")
+    _check(state, "state", (torch.float32,), 3)
+    _need(state.shape[1:] == (taps - 1, channels), f"state must be [slots, {taps - 1}, {channels}]")
+    for name, tensor in (("token_request", token_request), ("row_start", row_start), ("row_length", row_length),
+                         ("request_slots", request_slots)):
+        _check(tensor, name, (torch.int32,), 1)
+    rows = row_start.numel()
+    _need(token_request.numel() == tokens and row_length.numel() == rows and request_slots.numel() >= rows,
+          "the step's integer lists do not fit its tokens and rows")
+    _need(activation in (None, "silu"), f"unknown activation {activation!r}")
+    out = torch.empty((tokens, channels), dtype=x.dtype, device=x.device)
+    _call("mxb_short_conv", x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), state.data_ptr(),
+          token_request.data_ptr(), row_start.data_ptr(), row_length.data_ptr(), request_slots.data_ptr(),
+          out.data_ptr(), tokens, rows, channels, taps, state.shape[0], 1 if residual else 0,
+          1 if activation == "silu" else 0, _CODES[x.dtype], status_word(x.device).data_ptr(), _stream())
+    return out
+
+
+# ------------------------------------------------ selective state-space scan
+SCAN_STATES = 256   # the most states per channel the scan keeps in registers
+
+
+def selective_scan(x: torch.Tensor, step: torch.Tensor, step_bias: torch.Tensor, a: torch.Tensor, b: torch.Tensor,
+                   c: torch.Tensor, d: torch.Tensor, z: torch.Tensor, state: torch.Tensor, row_start: torch.Tensor,
+                   row_length: torch.Tensor, request_slots: torch.Tensor) -> torch.Tensor:
+    """S <- exp(dt A) S + dt x B, y = S C + D x, out = y silu(z) per channel,
+    token by token along each request row, dt = softplus(step + step_bias).
+    x, z ``[tokens, channels]`` and b, c ``[tokens, states]`` in the compute
+    type (rows may be strided; b and c share a row stride); ``step`` float32
+    ``[tokens, channels]``; ``a`` float32 ``[channels, states]``; ``state``
+    float32 ``[slots, channels, states]``, read and moved on."""
+    dtype = x.dtype
+    for name, tensor in (("x", x), ("z", z), ("b", b), ("c", c)):
+        _need(tensor.is_cuda and tensor.dtype == dtype and dtype in _CODES and tensor.dim() == 2
+              and tensor.stride(1) == 1, f"{name} must be a CUDA [tokens, width] tensor with unit column stride")
+    tokens, channels = x.shape
+    states = b.shape[1]
+    _need(z.shape == x.shape and c.shape == b.shape and b.shape[0] == tokens and b.stride(0) == c.stride(0),
+          "x, z, b and c do not fit one another")
+    _need(0 < states <= SCAN_STATES, f"{states} states per channel; up to {SCAN_STATES} are taken")
+    _need(step.is_cuda and step.dtype == torch.float32 and step.shape == x.shape and step.stride(1) == 1,
+          "step must be float32 [tokens, channels]")
+    _check(step_bias, "step_bias", (torch.float32,), 1)
+    _check(d, "d", (torch.float32,), 1)
+    _check(a, "a", (torch.float32,), 2)
+    _check(state, "state", (torch.float32,), 3)
+    _need(step_bias.numel() == channels and d.numel() == channels and a.shape == (channels, states)
+          and state.shape[1:] == (channels, states), "the scan's parameters or state do not fit its channels and states")
+    for name, tensor in (("row_start", row_start), ("row_length", row_length), ("request_slots", request_slots)):
+        _check(tensor, name, (torch.int32,), 1)
+    rows = row_start.numel()
+    _need(row_length.numel() == rows and request_slots.numel() >= rows, "the step's row lists differ in length")
+    out = torch.empty((tokens, channels), dtype=dtype, device=x.device)
+    _call("mxb_selective_scan", x.data_ptr(), x.stride(0), step.data_ptr(), step.stride(0), step_bias.data_ptr(),
+          a.data_ptr(), b.data_ptr(), c.data_ptr(), b.stride(0), d.data_ptr(), z.data_ptr(), z.stride(0),
+          state.data_ptr(), row_start.data_ptr(), row_length.data_ptr(), request_slots.data_ptr(), out.data_ptr(),
+          rows, channels, states, state.shape[0], _CODES[dtype], status_word(x.device).data_ptr(), _stream())
+    return out
+
+
+# ------------------------------------------------------------ routed experts
+ROUTER_OUTPUTS = 1024   # the most router outputs the routing kernel keeps in shared memory
+
+
+def route_experts(logits: torch.Tensor, correction: torch.Tensor, experts: int, top: int):
+    """Softmax over all router outputs, the ``top`` largest score + correction
+    chosen, weights = the chosen scores over their sum. Returns (chosen int32
+    ``[tokens, top]``, weights float32 ``[tokens, top]``, dense float32
+    ``[tokens, experts]`` with each real expert's weight or zero, float32
+    ``[tokens]`` weight that fell on the outputs from ``experts`` on, which
+    stand for experts that return their input)."""
+    _check(logits, "logits", (torch.float32,), 2)
+    _check(correction, "correction", (torch.float32,), 1)
+    tokens, outputs = logits.shape
+    _need(correction.numel() == outputs and 0 <= experts <= outputs and 0 < top <= outputs
+          and outputs <= ROUTER_OUTPUTS, "the router's sizes do not fit")
+    device = logits.device
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=device)
+    dense = torch.empty((tokens, experts), dtype=torch.float32, device=device)
+    on_identity = torch.empty((tokens,), dtype=torch.float32, device=device)
+    _call("mxb_route_experts", logits.data_ptr(), correction.data_ptr(), chosen.data_ptr(), weights.data_ptr(),
+          dense.data_ptr(), on_identity.data_ptr(), tokens, outputs, experts, top, _stream())
+    return chosen, weights, dense, on_identity
+
+
+def experts_dense_act(up: torch.Tensor, dense: torch.Tensor, ff: int) -> torch.Tensor:
+    """relu(up)^2 with column e * ff + f of token t times dense[t, e]."""
+    _check(up, "up", tuple(_CODES), 2)
+    _check(dense, "dense", (torch.float32,), 2)
+    tokens, experts = dense.shape
+    _need(up.shape == (tokens, experts * ff), "up must be [tokens, experts * ff]")
+    out = torch.empty_like(up)
+    _call("mxb_experts_dense_act", up.data_ptr(), dense.data_ptr(), out.data_ptr(), tokens, experts, ff,
+          _CODES[up.dtype], _stream())
+    return out
+
+
+def experts_add_identity(y: torch.Tensor, h: torch.Tensor, on_identity: torch.Tensor) -> torch.Tensor:
+    """y[t] += on_identity[t] * h[t] (y float32, in place)."""
+    _check(y, "y", (torch.float32,), 2)
+    _check(h, "h", tuple(_CODES), 2)
+    _check(on_identity, "on_identity", (torch.float32,), 1)
+    _need(h.shape == y.shape and on_identity.numel() == y.shape[0], "y, h and the weights do not fit")
+    _call("mxb_experts_add_identity", y.data_ptr(), h.data_ptr(), on_identity.data_ptr(), y.shape[0], y.shape[1],
+          _CODES[h.dtype], _stream())
+    return y
+
+
+def experts_routed(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor,
+                   weights: torch.Tensor, experts: int, ff: int) -> torch.Tensor:
+    """sum_k weight[t, k] W_down[e] relu(W_up[e] h_t)^2 over a token's chosen
+    experts e = chosen[t, k] < experts, plus h_t times the weights of chosen
+    indices from ``experts`` on; float32 ``[tokens, hidden]``. Only the chosen
+    experts' weights are read. w_up ``[experts * ff, hidden]``, w_down
+    ``[hidden, experts * ff]``."""
+    dtype = h.dtype
+    _check(h, "h", tuple(_CODES), 2)
+    _check(w_up, "w_up", (dtype,), 2)
+    _check(w_down, "w_down", (dtype,), 2)
+    _check(chosen, "chosen", (torch.int32,), 2)
+    _check(weights, "weights", (torch.float32,), 2)
+    tokens, hidden = h.shape
+    top = chosen.shape[1]
+    _need(chosen.shape == (tokens, top) and weights.shape == (tokens, top), "chosen and weights must be [tokens, top]")
+    _need(w_up.shape == (experts * ff, hidden) and w_down.shape == (hidden, experts * ff),
+          "the experts' stacked weights do not fit")
+    act = torch.empty((tokens * top, ff), dtype=torch.float32, device=h.device)
+    y = torch.empty((tokens, hidden), dtype=torch.float32, device=h.device)
+    _call("mxb_experts_routed", h.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), chosen.data_ptr(),
+          weights.data_ptr(), act.data_ptr(), y.data_ptr(), tokens, hidden, experts, ff, top, _CODES[dtype], _stream())
+    return y
+
+
+# ------------------------------------------------------ input from the token
+def add_cast(x: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """x += delta in float32 (in place; nothing is added without a delta);
+    returns x in ``out_dtype``."""
+    _check(x, "x", (torch.float32,))
+    if delta is not None:
+        _check(delta, "delta", tuple(_CODES))
+        _need(delta.shape == x.shape, "delta and x differ in shape")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _need(out_dtype in _CODES, "out_dtype must be float32 or bfloat16")
+    _call("mxb_add_cast", x.data_ptr(), _ptr(delta), _CODES[delta.dtype] if delta is not None else F32,
+          out.data_ptr(), _CODES[out_dtype], x.numel(), _stream())
+    return out
+
+
+def gelu_gate_rows(gate: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, offset: int) -> torch.Tensor:
+    """gelu_tanh(gate[t]) * table[ids[t], offset : offset + dim] for gate ``[tokens, dim]``."""
+    _check(gate, "gate", tuple(_CODES), 2)
+    _check(table, "table", (gate.dtype,), 2)
+    _check(ids, "ids", (torch.int32,), 1)
+    tokens, dim = gate.shape
+    _need(ids.numel() == tokens and 0 <= offset and offset + dim <= table.shape[1], "the table's columns do not fit")
+    out = torch.empty_like(gate)
+    _call("mxb_gelu_gate_rows", gate.data_ptr(), table.data_ptr(), ids.data_ptr(), out.data_ptr(), tokens, dim,
+          table.shape[1], offset, table.shape[0], _CODES[gate.dtype], status_word(gate.device).data_ptr(), _stream())
     return out
 
 
@@ -724,7 +916,7 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
                          tile_start: torch.Tensor, tile_length: torch.Tensor,
                          positions: torch.Tensor, scale: float, window: int = 0, chunk: int = 0,
                          gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                         gate_per_head: bool = False) -> torch.Tensor:
+                         gate_per_head: bool = False, sink: Optional[float] = None) -> torch.Tensor:
     """Attention of every query token over its request's cached keys (itself
     included) in float32; q is [tokens, heads, head_dim], out
     [tokens, heads, value_dim] with value_dim at most head_dim (the first
@@ -736,7 +928,9 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
     ``softcap`` c: scores pass c tanh(s / c) ahead of the softmax;
     ``gate`` ([tokens, heads * value_dim], or [tokens, heads] with
     ``gate_per_head``; rows may be strided): the output is multiplied by
-    sigmoid(gate) as it is written."""
+    sigmoid(gate) as it is written; ``sink``: the score of one more key that
+    has no value and that every query sees (0.0: one more in the softmax's
+    denominator)."""
     dtype = q.dtype
     _check(q, "q", tuple(_CODES), 3)
     _check(out, "out", (dtype,), 3)
@@ -767,7 +961,7 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
           tile_start.data_ptr(), tile_length.data_ptr(), positions.data_ptr(), tiles, heads,
           kv_heads, head_dim, page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[dtype],
           _ptr(gate), gate_stride, planes, value_dim, float(softcap), 1 if gate_per_head else 0,
-          status_word(q.device).data_ptr(), _stream())
+          0 if sink is None else 1, float(sink or 0.0), status_word(q.device).data_ptr(), _stream())
     return out
 
 

@@ -18,7 +18,12 @@ scores, s <- c tanh(s / c), ahead of the softmax; ``value_dim`` lets the
 values be wider or narrower than the keys (a page then holds rows as wide as
 the wider of the two, the others padded with zeros). Values of another width
 than the keys run on the general kernel only; a per-head gate is spread over
-the head's values for the tensor-core kernels.
+the head's values for the tensor-core kernels. ``sink`` adds one more key
+without a value to every query's softmax, with that score (0.0: the
+denominator is 1 + the sum). ``value_position`` (a rotary position part over
+the values' width) turns the value of position j by j before it is cached and
+turns each head's output at position i back by i, so that what a query takes
+from a value depends on their distance.
 
 Every size and constant is a parameter. When the head norms are RMSNorms (or
 absent) and the position encoding offers cos/sin tables (or is absent), norm,
@@ -130,7 +135,7 @@ def tiles_of(ctx: StepContext) -> Dict[str, object]:
 
 def attend_cached(q_heads: torch.Tensor, cache: CacheView, ctx: StepContext, *, scale: float, window: int = 0,
                   chunk: int = 0, softcap: float = 0.0, gate: Optional[torch.Tensor] = None, gate_per_head: bool = False,
-                  split_decode: bool = False, flash: bool = False, project=None):
+                  split_decode: bool = False, flash: bool = False, project=None, sink: Optional[float] = None):
     """Attention of a step's queries ``[tokens, heads, head_dim]`` over what the
     cache entry holds (this step's rows included), each kind of request on the
     kernel made for it: single tokens split along the keys, portions of prompts
@@ -172,7 +177,8 @@ def attend_cached(q_heads: torch.Tensor, cache: CacheView, ctx: StepContext, *, 
     if rest is not None and tiles["tile_request"][rest].numel():
         ops.paged_attention_tile(q_heads, cache.pool, out, cache.block_tables, tiles["tile_request"][rest],
                                  tiles["tile_start"][rest], tiles["tile_length"][rest], ctx.positions,
-                                 scale, window, chunk, gate=gate, softcap=softcap, gate_per_head=gate_per_head)
+                                 scale, window, chunk, gate=gate, softcap=softcap, gate_per_head=gate_per_head,
+                                 sink=sink)
     return out, False
 
 
@@ -236,6 +242,13 @@ class GQAttention:
         self.q_norm = build_part("norm", spec.get("q_norm"), weights, runtime)
         self.k_norm = build_part("norm", spec.get("k_norm"), weights, runtime)
         self.position = build_part("position", spec.get("position"), weights, runtime)
+        self.sink = None if spec.get("sink") is None else float(spec["sink"])
+        self.value_position = build_part("position", spec.get("value_position"), weights, runtime)
+        if self.value_position is not None:
+            if not getattr(self.value_position, "fused_tables", False) or self.value_position.head_dim != self.value_dim:
+                raise ValueError("value_position must be a rotary part with cos/sin tables over value_dim")
+            if self.gated:
+                raise ValueError("an output gate inside the attention kernels cannot follow the values' turn back")
         for name, norm, width in (("q_norm", self.q_norm, self.q_size), ("k_norm", self.k_norm, self.kv_size)):
             expected = self.head_dim if self.norm_scope == "head" else width
             if norm is not None and getattr(norm, "size", expected) != expected:
@@ -246,7 +259,7 @@ class GQAttention:
         position_fuses = self.position is None or getattr(self.position, "fused_tables", False)
         self.dtype = runtime.dtype
         # What only the general kernel does: values of another width than the keys.
-        self.general_only = self.value_dim != self.head_dim
+        self.general_only = self.value_dim != self.head_dim or self.sink is not None
         self.fused = norms_fuse and eps_agree and position_fuses and self.value_dim == self.head_dim
         self.split_decode = not self.general_only and ops.decode_attention_supported(
             self.head_dim, self.num_heads, self.num_kv_heads, self.dtype)
@@ -258,7 +271,13 @@ class GQAttention:
                          window=self.window or None, chunk=self.chunk or None)
 
     def parts(self):
-        return [self.q_norm, self.k_norm, self.position]
+        return [self.q_norm, self.k_norm, self.position, self.value_position]
+
+    def _turn_values(self, v: torch.Tensor, ctx: StepContext, back: bool = False) -> torch.Tensor:
+        """``[tokens, n * value_dim]`` turned by each token's position (``back``: by minus it)."""
+        turn = self.value_position
+        return ops.norm_rotate_heads(v, self.value_dim, ctx.positions, cos=turn.cos,
+                                     sin=turn.inverse_sin() if back else turn.sin, interleaved=turn.interleaved)
 
     def _tiles(self, ctx: StepContext) -> Dict[str, object]:
         return tiles_of(ctx)
@@ -281,6 +300,8 @@ class GQAttention:
         v = qkv[:, self.q_size + self.kv_size:self.q_size + self.kv_size + self.v_size] if self.own_values else k
         gate = qkv[:, self.gate_offset:self.gate_offset + self.gate_rows] if self.gated else None
         per_head = self.norm_scope == "head"
+        if self.value_position is not None:     # cached turned by their own position
+            v = self._turn_values(v, ctx).view(tokens, self.v_size)
         if self.value_dim != self.head_dim:
             return self._attend_unequal(x, q, k, v, gate, ctx, cache)
         q_heads = torch.empty((tokens, self.num_heads, self.head_dim), dtype=self.dtype, device=x.device)
@@ -321,8 +342,12 @@ class GQAttention:
         out, projected = attend_cached(
             q_heads, cache, ctx, scale=self.scale, window=self.window, chunk=self.chunk, softcap=self.softcap, gate=gate,
             gate_per_head=per_head_gate, split_decode=self.split_decode, flash=self.flash,
-            project=self.o if summands else None)
-        return out if projected else self.o.forward(out.view(tokens, self.q_size))
+            project=self.o if summands and self.value_position is None else None, sink=self.sink)
+        if projected:
+            return out
+        if self.value_position is not None:
+            out = self._turn_values(out.view(tokens, self.q_size), ctx, back=True)
+        return self.o.forward(out.view(tokens, self.q_size))
 
     def _attend_unequal(self, x, q, k, v, gate, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         """Values wider or narrower than the keys: a cached row is as wide as
@@ -357,7 +382,9 @@ class GQAttention:
         ops.paged_attention_tile(q_rows, cache.pool, out, cache.block_tables, tiles["tile_request"],
                                  tiles["tile_start"], tiles["tile_length"], ctx.positions, self.scale, self.window,
                                  self.chunk, gate=gate, softcap=self.softcap,
-                                 gate_per_head=self.gate_scope == "head")
+                                 gate_per_head=self.gate_scope == "head", sink=self.sink)
+        if self.value_position is not None:
+            out = self._turn_values(out.view(tokens, self.out_size), ctx, back=True)
         return self.o.forward(out.view(tokens, self.out_size))
 
     def weight_bytes(self) -> int:

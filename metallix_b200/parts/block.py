@@ -19,6 +19,12 @@ runs on norm(u), and its result y, times a per-channel layer scale, goes back
 to all streams at once: x_t <- sum_s mix_q[s, t] x_s + out_q[t] y. What a
 sublayer leaves is handed on as a ``StreamWrite``; the write, the next read
 and (when it is elementwise) the next norm are one kernel.
+
+``conv_prenorm_residual`` is the pre-norm layer with two additions, each
+optional: what a sublayer reads passes a short causal convolution over time
+first (h <- h + conv(h), whose last inputs are part of a request's state),
+and after the feed-forward the layer takes an input from the token itself,
+x <- x + norm(input(x, token)).
 """
 from __future__ import annotations
 
@@ -216,3 +222,63 @@ class HyperConnectionBlock:
 
 register_part("block", "hyper_connections",
               lambda layer, weights, runtime: HyperConnectionBlock(layer, weights, runtime))
+
+
+class ConvPreNormBlock:
+    """x <- x + mixer(c1(norm1(x))); x <- x + ff(c2(norm2(x))); x <- x + norm(token_input(x, token)), with
+    c(h) = h + conv(h). The convolutions' states join the mixer's own need as members of one cache entry:
+    [mixer, mixer's convolution, feed-forward's convolution] as far as they exist."""
+
+    kind = "conv_prenorm_residual"
+
+    def __init__(self, layer: LayerSpec, weights: WeightStore, runtime: Runtime):
+        from .short_conv import ShortConv
+        from .token_input import TokenInput
+        params = layer.block
+        self.name = layer.name
+        self.mixer_norm = build_part("norm", layer.mixer_norm, weights, runtime)
+        self.mixer = build_part("mixer", layer.mixer, weights, runtime)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, runtime)
+        self.feed_forward_norm = None
+        if self.feed_forward is not None:
+            if layer.feed_forward_norm is None:
+                raise ValueError(f"{layer.name}: a feed-forward needs its norm")
+            self.feed_forward_norm = build_part("norm", layer.feed_forward_norm, weights, runtime)
+        conv = lambda key: ShortConv(params[key], weights, runtime) if params.get(key) is not None else None
+        self.mixer_conv = conv("mixer_conv")
+        self.feed_forward_conv = conv("feed_forward_conv") if self.feed_forward is not None else None
+        self.token_input = TokenInput(params["token_input"], weights, runtime) \
+            if params.get("token_input") is not None else None
+        self.dtype = runtime.dtype
+        self._members = [self.mixer] + [c for c in (self.mixer_conv, self.feed_forward_conv) if c is not None]
+
+    def parts(self):
+        return [self.mixer_norm, self.mixer_conv, self.mixer, self.feed_forward_norm, self.feed_forward_conv,
+                self.feed_forward, self.token_input]
+
+    def cache_need(self):
+        from ..config.spec import CacheNeed
+        return CacheNeed(kind="several", members=tuple(part.cache_need() for part in self._members))
+
+    def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: CacheView):
+        views = list(cache.members)
+        if len(views) != len(self._members):
+            raise ValueError(f"{self.name}: the cache entry has {len(views)} members, the layer needs {len(self._members)}")
+        own, at = views[0], 1
+        read = self.mixer_norm.add_forward(residual, pending, self.dtype)
+        if self.mixer_conv is not None:
+            read = self.mixer_conv.forward(read, ctx, views[at])
+            at += 1
+        left = self.mixer.forward(read, ctx, own)
+        if self.feed_forward is not None:
+            read = self.feed_forward_norm.add_forward(residual, left, self.dtype)
+            if self.feed_forward_conv is not None:
+                read = self.feed_forward_conv.forward(read, ctx, views[at])
+            left = self.feed_forward.forward(read, ctx)
+        if self.token_input is None:
+            return left
+        return self.token_input.forward(residual, left, ctx)
+
+
+register_part("block", "conv_prenorm_residual",
+              lambda layer, weights, runtime: ConvPreNormBlock(layer, weights, runtime))

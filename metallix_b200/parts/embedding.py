@@ -24,9 +24,10 @@ class TokenEmbedding:
         self.table = table.to(device=runtime.device, dtype=runtime.dtype).contiguous()
         self.vocab_size = spec["vocab_size"]
         self.name = spec["weight"]
+        self.scale = float(spec.get("scale") or 1.0)   # the rows leave multiplied by it, in float32
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
-        return ops.embed(ids, self.table)
+        return ops.embed(ids, self.table, scale=self.scale)
 
     def weight_bytes(self) -> int:
         return self.table.numel() * self.table.element_size()

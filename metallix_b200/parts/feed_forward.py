@@ -4,7 +4,13 @@ are stacked so that one product yields both; SiLU and the product with u are
 float32 inside the kernel.
 
 ``dense_ff`` is the feed-forward without a gate: d = act(m Wu^T) Wd^T, the
-activation a parameter (``relu_squared``: max(z, 0)^2)."""
+activation a parameter (``relu_squared``: max(z, 0)^2).
+
+``routed_experts`` is a mixture of such feed-forwards: a router picks ``top``
+of ``experts`` (+ ``identity`` outputs that stand for experts returning their
+input) per token by softmax score plus a correction, and the output is the sum
+of the chosen experts' outputs weighted by their scores over the chosen
+scores' sum."""
 from __future__ import annotations
 
 import torch
@@ -83,3 +89,66 @@ class DenseFeedForward:
 
 
 register_part("feed_forward", "dense_ff", lambda spec, weights, runtime: DenseFeedForward(spec, weights, runtime))
+
+
+class RoutedExperts:
+    """z = m Wr^T (float32); s = softmax(z) over all experts + identity
+    outputs; the ``top`` largest s + correction are chosen; weights are the
+    chosen s over their sum (+ 1e-20); d = sum_k weight_k expert_k(m), an
+    expert being Wdown act(Wup m) or, for the last ``identity`` outputs, m
+    itself. Steps of up to ``ROUTED_TOKENS`` tokens read only the chosen
+    experts' weights; larger ones run all experts as two stacked products with
+    the weights (zero for experts not chosen) applied in between."""
+
+    kind = "routed_experts"
+    ROUTED_TOKENS = 16
+    ACTIVATIONS = ("relu_squared",)
+
+    def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
+        hidden, ff = spec["hidden_size"], spec["intermediate_size"]
+        self.experts, self.identity, self.top = int(spec["experts"]), int(spec.get("identity") or 0), int(spec["top"])
+        outputs = self.experts + self.identity
+        if not 0 < self.top <= outputs or outputs > ops.ROUTER_OUTPUTS:
+            raise ValueError(f"top {self.top} of {outputs} router outputs (at most {ops.ROUTER_OUTPUTS}) cannot be chosen")
+        if spec["activation"] not in self.ACTIVATIONS:
+            raise ValueError(f"activation {spec['activation']!r}; one of {self.ACTIVATIONS}")
+        ups, downs = [], []
+        for index in range(self.experts):
+            up, down = weights.take(spec["up_proj"].format(index)), weights.take(spec["down_proj"].format(index))
+            if tuple(up.shape) != (ff, hidden) or tuple(down.shape) != (hidden, ff):
+                raise ValueError(f"expert {index}: up is {tuple(up.shape)}, down is {tuple(down.shape)}; "
+                                 f"expected {(ff, hidden)} and {(hidden, ff)}")
+            ups.append(up.to(runtime.device))
+            downs.append(down.to(runtime.device))
+        # up: rows e * ff + f; down: columns e * ff + f, so that an expert's block of a row is contiguous
+        self.up = Linear(torch.cat(ups, dim=0), runtime) if ups else None
+        self.down = Linear(torch.cat(downs, dim=1), runtime) if downs else None
+        router = weights.take(spec["router"])
+        if tuple(router.shape) != (outputs, hidden):
+            raise ValueError(f"{spec['router']} is {tuple(router.shape)}, expected {(outputs, hidden)}")
+        self.router = Linear(router, runtime)
+        correction = weights.take(spec["correction"]) if spec.get("correction") else torch.zeros(outputs)
+        if correction.numel() != outputs:
+            raise ValueError(f"{spec['correction']} has {correction.numel()} values, expected {outputs}")
+        self.correction = correction.to(device=runtime.device, dtype=torch.float32).reshape(-1).contiguous()
+        self.hidden_size, self.intermediate_size = hidden, ff
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """float32 ``[tokens, hidden]``."""
+        logits = self.router.forward(x, out_dtype=torch.float32)
+        chosen, weights, dense, on_identity = ops.route_experts(logits, self.correction, self.experts, self.top)
+        if self.up is None:     # identity experts only
+            return ops.experts_add_identity(torch.zeros(x.shape, dtype=torch.float32, device=x.device), x, on_identity)
+        if x.shape[0] <= self.ROUTED_TOKENS:
+            return ops.experts_routed(x, self.up.weight, self.down.weight, chosen, weights, self.experts,
+                                      self.intermediate_size)
+        act = ops.experts_dense_act(self.up.forward(x), dense, self.intermediate_size)
+        return ops.experts_add_identity(self.down.forward(act, out_dtype=torch.float32), x, on_identity)
+
+    def weight_bytes(self) -> int:
+        """What a decode step of one token reads: the router and ``top`` experts."""
+        per_expert = (self.up.weight_bytes() + self.down.weight_bytes()) // self.experts if self.up is not None else 0
+        return self.router.weight_bytes() + min(self.top, self.experts) * per_expert
+
+
+register_part("feed_forward", "routed_experts", lambda spec, weights, runtime: RoutedExperts(spec, weights, runtime))

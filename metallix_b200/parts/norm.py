@@ -2,7 +2,8 @@
 directly (crates/models/qwen/src/forward.rs:2442-2449). Sum of squares and
 scale are float32 in both precisions. A checkpoint may store the weight around
 zero (``one_plus``): the factor is then 1 + w, formed once in float32 when the
-part is built.
+part is built. It may also store one number for all coordinates (``scalar``)
+or none at all (the row over its root mean square).
 
 Dynamic Tanh: y = tanh(alpha * x) * w + b with a scalar alpha, computed value
 by value in float32; it takes no mean or variance of the row, so it has no
@@ -54,7 +55,15 @@ class RMSNorm:
 
 
 def _build(spec: PartSpec, weights: WeightStore, runtime: Runtime) -> RMSNorm:
+    """``weight`` None: the row over its root mean square and nothing else;
+    ``scalar``: the stored weight is one number for all coordinates."""
+    if spec.get("weight") is None:
+        return RMSNorm(torch.ones(spec["size"]), spec["eps"], runtime)
     weight = weights.take(spec["weight"])
+    if spec.get("scalar"):
+        if weight.numel() != 1:
+            raise ValueError(f"{spec['weight']} has {weight.numel()} values, a scalar norm weight has one")
+        weight = weight.to(torch.float32).reshape(1).expand(spec["size"])
     if weight.numel() != spec["size"]:
         raise ValueError(f"{spec['weight']} has {weight.numel()} values, the norm is over {spec['size']}")
     return RMSNorm(weight, spec["eps"], runtime, one_plus=bool(spec.get("one_plus", False)))

@@ -72,6 +72,14 @@ class Rotary:
             runtime.shared[key] = (torch.cos(angle).to(torch.float32).contiguous(),
                                    torch.sin(angle).to(torch.float32).contiguous())
         self.cos, self.sin = runtime.shared[key]
+        self._shared, self._key = runtime.shared, key
+
+    def inverse_sin(self) -> torch.Tensor:
+        """The sine table of the turn back (by minus the position), made at first use and shared like the others."""
+        key = self._key + ("inverse",)
+        if key not in self._shared:
+            self._shared[key] = (-self.sin).contiguous()
+        return self._shared[key]
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor):
         """Rotates q [tokens, heads * head_dim] and k [tokens, kv_heads * head_dim];

@@ -49,6 +49,21 @@ def request_rows(plan: StepPlan) -> Prepared:
                     {"longest": longest}, graph_key=longest >= 8)
 
 
+def request_rows_of(ctx: StepContext) -> Dict[str, torch.Tensor]:
+    """The step's request rows: what the engine prepared, or (for a caller that
+    built a context by hand) made here from the host lists."""
+    rows = ctx.extras.get("request_rows")
+    if rows is None:
+        if ctx.request_offsets is None:
+            raise ValueError("the request rows were not prepared for this step")
+        counts = [ctx.request_offsets[row + 1] - ctx.request_offsets[row] for row in range(ctx.num_requests)]
+        prepared = request_rows(StepPlan(counts, ctx.request_positions, len(counts), 0))
+        rows = dict(prepared.facts)
+        rows.update({name: torch.from_numpy(array).to(ctx.device) for name, array in prepared.arrays.items()})
+        ctx.extras["request_rows"] = rows
+    return rows
+
+
 class MatrixMemory:
     kind = "mlstm"
     graph_safe = True
@@ -92,16 +107,7 @@ class MatrixMemory:
         return CacheNeed(kind="state", state_shape=(self.state_values,), state_dtype="float32")
 
     def _rows(self, ctx: StepContext) -> Dict[str, torch.Tensor]:
-        rows = ctx.extras.get(self.step_key)
-        if rows is None:
-            if ctx.request_offsets is None:
-                raise ValueError("the recurrence's request rows were not prepared for this step")
-            counts = [ctx.request_offsets[row + 1] - ctx.request_offsets[row] for row in range(ctx.num_requests)]
-            prepared = request_rows(StepPlan(counts, ctx.request_positions, len(counts), 0))
-            rows = dict(prepared.facts)
-            rows.update({name: torch.from_numpy(array).to(ctx.device) for name, array in prepared.arrays.items()})
-            ctx.extras[self.step_key] = rows
-        return rows
+        return request_rows_of(ctx)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
         if cache.state is None:
@@ -121,3 +127,86 @@ class MatrixMemory:
 
 
 register_part("mixer", "mlstm", lambda spec, weights, runtime: MatrixMemory(spec, weights, runtime))
+
+
+class SelectiveScan:
+    """The selective state-space mixer (Mamba): a Win^T = [x | z]; x passes a
+    short causal convolution with bias and silu; x Wx^T = [dt | B | C] with a
+    low-rank step size dt <- softplus(dt Wdt^T + b); A = -exp(A_log); per
+    channel c and state n
+
+        S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n,    y_c = sum_n S[c, n] C_n + D_c x_c;
+
+    then y * silu(z) and the output projection. The state S (float32,
+    ``[inner, states]``), and the convolution's last inputs, are kept per request
+    in the cache's state slots. Step sizes, decays and the recurrence are
+    float32 in both precisions (the step size's product leaves in float32);
+    the projections, the convolution and what they hand on are in the compute
+    type."""
+
+    kind = "selective_scan"
+    graph_safe = True
+    step_key = "request_rows"
+    prepare_step = staticmethod(request_rows)
+
+    def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
+        from .short_conv import ShortConv
+        hidden = spec["hidden_size"]
+        self.inner, self.states, self.rank = int(spec["inner_size"]), int(spec["state_size"]), int(spec["step_rank"])
+        if not 0 < self.states <= ops.SCAN_STATES:
+            raise ValueError(f"{self.states} states per channel; the scan takes up to {ops.SCAN_STATES}")
+
+        def matrix(name, shape):
+            weight = weights.take(spec[name])
+            if tuple(weight.shape) != shape:
+                raise ValueError(f"{spec[name]} is {tuple(weight.shape)}, expected {shape}")
+            return weight
+
+        def vector(name, size):
+            tensor = weights.take(spec[name])
+            if tensor.numel() != size:
+                raise ValueError(f"{spec[name]} has {tensor.numel()} values, expected {size}")
+            return tensor.to(device=runtime.device, dtype=torch.float32).reshape(-1).contiguous()
+
+        self.inputs = Linear(matrix("in_proj", (2 * self.inner, hidden)), runtime)      # rows: x, then z
+        self.conv = ShortConv(PartSpec("short_conv", {
+            "channels": self.inner, "taps": int(spec["conv_taps"]), "weight": spec["conv_weight"],
+            "bias": spec.get("conv_bias"), "activation": "silu"}), weights, runtime)
+        self.selectors = Linear(matrix("x_proj", (self.rank + 2 * self.states, self.inner)), runtime)   # dt, B, C
+        self.step = Linear(matrix("step_proj", (self.inner, self.rank)), runtime)
+        self.step_bias = vector("step_bias", self.inner)
+        a_log = matrix("a_log", (self.inner, self.states))
+        self.decay = (-torch.exp(a_log.to(device=runtime.device, dtype=torch.float32))).contiguous()
+        self.skip = vector("skip", self.inner)
+        self.o = Linear(matrix("o_proj", (hidden, self.inner)), runtime)
+        self.dtype = runtime.dtype
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kind="several", members=(
+            CacheNeed(kind="state", state_shape=(self.inner, self.states), state_dtype="float32"),
+            self.conv.cache_need()))
+
+    def parts(self):
+        return [self.conv]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        if len(cache.members) != 2 or cache.members[0].state is None:
+            raise ValueError("the selective scan needs its two state entries of the cache")
+        rows = request_rows_of(ctx)
+        both = self.inputs.forward(x)
+        u = self.conv.forward(both[:, :self.inner], ctx, cache.members[1])
+        picked = self.selectors.forward(u)
+        low = picked[:, :self.rank]
+        step = self.step.forward(low if low.is_contiguous() else low.contiguous(), out_dtype=torch.float32)
+        mixed = ops.selective_scan(
+            u, step, self.step_bias, self.decay, picked[:, self.rank:self.rank + self.states],
+            picked[:, self.rank + self.states:], self.skip, both[:, self.inner:], cache.members[0].state,
+            rows["row_start"], rows["row_length"], ctx.request_slots)
+        return self.o.forward(mixed)
+
+    def weight_bytes(self) -> int:
+        return (self.inputs.weight_bytes() + self.selectors.weight_bytes() + self.step.weight_bytes()
+                + self.o.weight_bytes() + self.decay.numel() * 4)
+
+
+register_part("mixer", "selective_scan", lambda spec, weights, runtime: SelectiveScan(spec, weights, runtime))

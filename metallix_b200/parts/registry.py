@@ -189,6 +189,7 @@ class StepContext:
     request_offsets: Optional[List[int]]    # host, [requests + 1]
     request_positions: Optional[List[int]]  # host, first position of each row's tokens
     extras: Dict[str, object] = field(default_factory=dict)
+    token_ids: Optional[torch.Tensor] = None   # int32 [tokens]: the step's token ids, for a part that reads a table by them
 
 
 def step_preparers(blocks) -> Dict[str, object]:
