@@ -7,6 +7,7 @@
     python bench.py --workload decode|prefill|gemm|attention|pick ...   small fixed workloads for profilers
     python bench.py --design mekazen                              the Mekazen decoder beside Qwen3 at equal layer sizes
     python bench.py --design zitezen                              the Zitezen decoder beside Qwen3 at equal width, heads and feed-forward
+    python bench.py --design sadosun                              the Sadosun decoder beside Qwen3 and Zitezen at equal width and active weights
 
 Default workload: a Qwen3-0.6B-shaped model (28 layers,
 hidden 1024, 16 query and 8 key/value heads of 128, SwiGLU 3072, vocabulary
@@ -664,6 +665,10 @@ def workload(args):
         if args.design == "zitezen":   # its layers come in fours: the first `layers` of them
             other = _zitezen(hidden, heads, kv_heads, dim, inter, {"0.6b": "0.6b-layers", "8b": "8b-layers"}[args.shape])
             config = parse_config(dict(other, layers=(other["layers"] * layers)[:layers]))
+        elif args.design == "sadosun":   # its layers come in twos
+            other = _sadosun(hidden, heads, kv_heads, dim, inter, {"0.6b": "0.6b-layers", "8b": "8b-layers"}[args.shape],
+                             args.chunk or 4096)
+            config = parse_config(dict(other, layers=(other["layers"] * layers)[:layers]))
         else:
             other = _mekazen(hidden, heads, kv_heads, dim, inter, args.chunk or 4096)
             config = parse_config(dict(other, layers=other["layers"][:1] * layers))
@@ -1064,6 +1069,239 @@ def design_zitezen(args):
     return 0
 
 
+# Sadosun layers at the two sizes: the state-space mixer's (inner channels, states, step rank, taps), the
+# experts' (count, identity experts, top, ff) with top * ff * 2 matrices = the dense model's 3 * inter, the
+# taps of the convolutions ahead of the sublayers and the width of a layer's input from the token. Eight
+# layers: a state-space layer and an attention layer in turn. The window is as long as the contexts by
+# default (--chunk), so that both models' attention does the same work.
+SADOSUN_SIZES = {"0.6b-layers": ((2048, 16, 64, 4), (16, 2, 4, 1152), 4, 64),
+                 "8b-layers": ((8192, 16, 256, 4), (16, 2, 4, 4608), 4, 256)}
+
+
+def _sadosun(hidden, heads, kv_heads, dim, inter, size, window):
+    scan, (count, identity, top, ff), taps, side = SADOSUN_SIZES[size]
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": count, "identity": identity, "top": top}}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                 "mask": {"size": window}, "rot": {"base": 1.0e4, "dims": dim}}
+    state_space = {"inner": scan[0], "state": scan[1], "dt_rank": scan[2], "conv": scan[3]}
+    pair = [{"type": "mamba1", "mixer": state_space, "mlp": mlp}, {"type": "attention", "mixer": attention, "mlp": mlp}]
+    return {"architecture": "Sadosun", "vocab": DESIGN_VOCAB, "width": hidden, "norm": {"eps": 1e-6},
+            "embedding": {"scale": hidden ** 0.5}, "canon": {"taps": taps}, "token_side": {"dim": side},
+            "layers": pair * (DESIGN_LAYERS // 2)}
+
+
+def design_sadosun(args):
+    """Prompt and decode throughput of the Sadosun decoder beside the Qwen3
+    decoder (equal width, heads and active feed-forward weights) and the
+    Zitezen decoder (the other model with a recurrent mixer), random weights,
+    bfloat16, 8 layers; then each kernel the design adds beside the like
+    kernel of those models: bytes that must move over time against the
+    measured copy bandwidth, or arithmetic over time against the measured
+    bf16 matrix peak. One JSON line."""
+    import numpy as np
+    import torch
+    from metallix_b200 import ops, parse_config
+    from metallix_b200.config.spec import PartSpec
+    from metallix_b200.parts.registry import Runtime, WeightStore, build_part
+
+    peak, peak_source = peaks()
+    warmup, steps = max(args.warmup, 3), min(max(args.steps, 1), 64)
+    rng = np.random.default_rng(0)
+    window = args.chunk or args.context
+    out = {"design": "sadosun", "beside": ["qwen3", "zitezen"], "dtype": "bf16", "layers": DESIGN_LAYERS,
+           "vocab": DESIGN_VOCAB, "prompt_len": args.prompt_len, "window": window, "peaks": peak_source, "sizes": {}}
+    for size, (hidden, heads, kv_heads, dim, inter) in ({} if args.kernels_only else DESIGN_SIZES).items():
+        configs = {"sadosun": parse_config(_sadosun(hidden, heads, kv_heads, dim, inter, size, window)),
+                   "qwen3": parse_config(dict(_qwen3(DESIGN_LAYERS, hidden, heads, kv_heads, inter, False),
+                                              vocab_size=DESIGN_VOCAB, head_dim=dim)),
+                   "zitezen": parse_config(_zitezen(hidden, heads, kv_heads, dim, inter, size))}
+        out["sizes"][size] = {family: _engine_numbers(config, args, peak, rng, warmup, steps)
+                              for family, config in configs.items()}
+
+    def measure(function):
+        for _ in range(3):
+            function()
+        flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+        times = []
+        for _ in range(7):
+            flush.zero_()    # a buffer larger than L2 between the timed launches
+            times.append(timed(torch, "cuda", lambda _: function(), 1))
+        return statistics.median(times)
+
+    def gbs(bytes_moved, function):
+        ms = measure(function)
+        return {"us": ms * 1e3, "gb_s": bytes_moved / (ms * 1e-3) / 1e9,
+                "frac_of_copy_bandwidth": bytes_moved / (ms * 1e-3) / 1e9 / peak["hbm_gbs"]}
+
+    def tflops(flops, function):
+        ms = measure(function)
+        return {"us": ms * 1e3, "tflop_s": flops / (ms * 1e-3) / 1e12,
+                "frac_of_bf16_matrix_peak": flops / (ms * 1e-3) / 1e12 / peak["bf16_tflops"]}
+
+    ops.require_cuda()
+    kernels = {}
+    size = "8b-layers"
+    hidden, heads, kv_heads, dim, inter = DESIGN_SIZES[size]
+    (inner, states, rank, scan_taps), (count, identity, top, ff), taps, side = SADOSUN_SIZES[size]
+    bf16, f32 = torch.bfloat16, torch.float32
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+    normal = lambda *shape: torch.randn(*shape, device="cuda")
+    prompt = args.prompt_len
+    runtime = Runtime(device=torch.device("cuda"), dtype=bf16, max_positions=args.context, gemm_backend=args.gemm)
+
+    def weights_of(shapes):
+        return WeightStore({name: (normal(*shape) * 0.02).to(bf16) for name, shape in shapes.items()})
+
+    def sink_attention(q, cache, out, table, tile_request, tile_start, tile_length, positions, longest):
+        """The kernel this design's attention part runs: a window, one more in the softmax's denominator."""
+        return ops.paged_attention_tile(q, cache, out, table, tile_request, tile_start, tile_length, positions,
+                                        dim ** -0.5, window, sink=0.0)
+
+    def prompt_tiles(tokens, tile=16):
+        starts = list(range(0, tokens, tile))
+        return ints([0] * len(starts)), ints(starts), ints([min(tile, tokens - s) for s in starts])
+
+    # ---- what a sublayer reads: the sum, the norm, and (this design) the convolution over time
+    for tokens in (8, prompt * 4):
+        x, delta, ones = normal(tokens, hidden), normal(tokens, hidden).to(bf16), torch.ones(hidden, device="cuda")
+        normed = normal(tokens, hidden).to(bf16)
+        conv_w, conv_state = normal(hidden, taps), torch.zeros(2, taps - 1, hidden, device="cuda")
+        owner, start, length, slot = ints([0] * tokens), ints([0]), ints([tokens]), ints([0])
+        if tokens == 8:     # eight requests of one token
+            owner, start, length, slot = ints(range(8)), ints(range(8)), ints([1] * 8), ints([0, 1] * 4)
+        kernels[f"sublayer_input_{tokens}"] = {
+            "sadosun: h + conv(h) over %d taps, the state moved on" % taps: gbs(
+                tokens * hidden * 2 * 2, lambda: ops.short_conv(normed, conv_w, None, conv_state, owner, start, length,
+                                                                slot, residual=True)),
+            "qwen3 (and sadosun): x += d; y = norm(x)": gbs(tokens * hidden * (4 + 4 + 2 + 2),
+                                                            lambda: ops.add_rmsnorm(x, delta, ones, 1e-6, bf16))}
+        gate, table = normal(tokens, side).to(bf16), normal(DESIGN_VOCAB, DESIGN_LAYERS * side).to(bf16)
+        ids = ints(rng.integers(0, DESIGN_VOCAB, size=tokens).tolist())
+        gate_up = normal(tokens, 2 * side).to(bf16)
+        kernels[f"gated_rows_{tokens}"] = {
+            "sadosun: gelu_tanh(gate) * the token's table columns": gbs(
+                tokens * side * 2 * 3, lambda: ops.gelu_gate_rows(gate, table, ids, side)),
+            "qwen3: silu(gate) * up": gbs(tokens * side * 2 * 3, lambda: ops.silu_mul(gate_up))}
+
+    # ---- the feed-forward: routed experts beside the dense feed-forward with as many active weights
+    names = {f"m.e{e}.{which}": (ff, hidden) if which == "up" else (hidden, ff) for e in range(count) for which in ("up", "down")}
+    names.update({"m.router": (count + identity, hidden)})
+    store = weights_of(names)
+    store._tensors["m.correction"] = torch.zeros(count + identity, device="cuda")
+    routed = build_part("feed_forward", PartSpec("routed_experts", {
+        "hidden_size": hidden, "intermediate_size": ff, "experts": count, "identity": identity, "top": top,
+        "activation": "relu_squared", "up_proj": "m.e{}.up", "down_proj": "m.e{}.down", "router": "m.router",
+        "correction": "m.correction"}), store, runtime)
+    dense = build_part("feed_forward", PartSpec("swiglu", {
+        "hidden_size": hidden, "intermediate_size": inter, "gate_proj": "g", "up_proj": "u", "down_proj": "d"}),
+        weights_of({"g": (inter, hidden), "u": (inter, hidden), "d": (hidden, inter)}), runtime)
+    del store
+    for tokens in (8, prompt * 4):
+        h = normal(tokens, hidden).to(bf16)
+        logits = routed.router.forward(h, out_dtype=f32)
+        chosen = ops.route_experts(logits, routed.correction, count, top)[0]
+        real = chosen[chosen < count]
+        pairs, distinct = int(real.numel()), int(torch.unique(real).numel())
+        label = f"feed_forward_{tokens}"
+        if tokens == 8:     # a decode step: the weights that must be read
+            kernels[label] = {
+                "sadosun: router, choice, %d distinct experts of %d" % (distinct, count): gbs(
+                    distinct * 2 * ff * hidden * 2 + (count + identity) * hidden * 2, lambda: routed.forward(h, None)),
+                "qwen3: gate, up, activation, down": gbs(3 * inter * hidden * 2, lambda: dense.forward(h, None))}
+        else:               # a prompt: the products that must be made
+            kernels[label] = {
+                "sadosun: router, choice, the chosen experts": tflops(
+                    pairs * 4.0 * ff * hidden + tokens * 2.0 * (count + identity) * hidden, lambda: routed.forward(h, None)),
+                "qwen3: gate, up, activation, down": tflops(tokens * 6.0 * inter * hidden, lambda: dense.forward(h, None))}
+    del routed, dense
+
+    # ---- a decode step's mixer over 8 requests: a state per request against cached keys and values
+    batch, context = 8, prompt
+    rows, one_each = ints(range(batch)), ints([1] * batch)
+    a = -torch.exp(normal(inner, states) * 0.5)
+    vector = lambda: normal(inner)
+    bias, skip = vector() - 3.0, vector()
+
+    def scan_inputs(tokens):
+        both = normal(tokens, 2 * inner).to(bf16)
+        picked = normal(tokens, rank + 2 * states).to(bf16)
+        return both, picked, normal(tokens, inner)
+
+    both, picked, step = scan_inputs(batch)
+    scan_state = torch.zeros(batch, inner, states, device="cuda")
+    kernels["decode_step_mixer_8_requests"] = {
+        "sadosun: selective scan, state read and written": gbs(
+            2 * scan_state.numel() * 4 + a.numel() * 4,
+            lambda: ops.selective_scan(both[:, :inner], step, bias, a, picked[:, rank:rank + states],
+                                       picked[:, rank + states:], skip, both[:, inner:], scan_state, rows, one_each, rows))}
+    memory = ZITEZEN_SIZES[size][0]
+    H, D, V = memory
+    width = 2 * H * D + 2 * H * V + 2 * H
+    proj = normal(batch, width) * 0.1
+    memory_state = torch.zeros(batch, ops.mlstm_state_values(H, D, V), device="cuda")
+    zeros = torch.zeros(H, device="cuda")
+    offsets = (0, H * D, 2 * H * D, 2 * H * D + 2 * H * V, 2 * H * D + 2 * H * V + H)
+    kernels["decode_step_mixer_8_requests"]["zitezen: matrix memory, state read and written"] = gbs(
+        2 * memory_state.numel() * 4, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 10.0, memory_state, rows,
+                                                             one_each, rows, H, D, V))
+    pages = batch * (-(-context // 16))
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").view(batch, -1)
+    positions = ints([context - 1] * batch)
+    cache = normal(pages, 2, kv_heads, 16, dim).to(bf16)
+    q = normal(batch, heads, dim).to(bf16)
+    attended = torch.empty_like(q)
+    kv_bytes = cache.numel() * 2
+    kernels["decode_step_mixer_8_requests"]["qwen3: split-key attention over %d cached positions" % context] = gbs(
+        kv_bytes, lambda: ops.paged_attention_decode(q, cache, attended, table, rows, rows, positions, dim ** -0.5,
+                                                     context))
+    kernels["decode_step_mixer_8_requests"]["sadosun: attention with a sink over the same rows"] = gbs(
+        kv_bytes, lambda: sink_attention(q, cache, attended, table, rows, rows, one_each, positions, context))
+
+    # ---- a prompt in one step
+    tokens = prompt
+    both, picked, step = scan_inputs(tokens)
+    scan_state.zero_()
+    one_row, length = ints([0]), ints([tokens])
+    kernels[f"prompt_mixer_{tokens}"] = {
+        "sadosun: selective scan of one request (rows read and written)": gbs(
+            tokens * inner * (2 + 4 + 2 + 2) + tokens * 2 * states * 2,
+            lambda: ops.selective_scan(both[:, :inner], step, bias, a, picked[:, rank:rank + states],
+                                       picked[:, rank + states:], skip, both[:, inner:], scan_state, one_row, length,
+                                       one_row))}
+    proj = normal(tokens, width) * 0.1
+    memory_state.zero_()
+    kernels[f"prompt_mixer_{tokens}"]["zitezen: matrix memory of one request, in chunks (rows read and written)"] = gbs(
+        tokens * (width * 4 + H * V * 4), lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 10.0, memory_state, one_row,
+                                                                 length, one_row, H, D, V, longest=tokens))
+    pages = -(-tokens // 16)
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, -1)
+    positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    cache = normal(pages, 2, kv_heads, 16, dim).to(bf16)
+    q = normal(tokens, heads, dim).to(bf16)
+    attended = torch.empty_like(q)
+    flops = 4.0 * dim * heads * tokens * (tokens + 1) / 2
+    tile = ops.flash_prefill_tile()
+    starts = list(range(0, tokens, tile))[::-1]
+    tiles = (ints([0] * len(starts)), ints(starts), ints([min(tile, tokens - s) for s in starts]))
+    kernels[f"prompt_mixer_{tokens}"]["qwen3: tensor-core attention"] = tflops(
+        flops, lambda: ops.flash_prefill(q, cache, attended, table, *tiles, positions, dim ** -0.5,
+                                         longest_context=tokens))
+    kernels[f"prompt_mixer_{tokens}"]["sadosun: attention with a sink"] = tflops(
+        flops, lambda: sink_attention(q, cache, attended, table, *prompt_tiles(tokens), positions, tokens))
+    v = normal(tokens, kv_heads * dim).to(bf16)
+    turn = build_part("position", PartSpec("rope_interleaved", {"theta": 1.0e4, "rotary_dim": dim, "head_dim": dim,
+                                                               "scaling": None}), WeightStore({}), runtime)
+    flat = attended.view(tokens, heads * dim)
+    kernels[f"prompt_mixer_{tokens}"]["sadosun: values turned by their position, outputs turned back"] = gbs(
+        tokens * (kv_heads + heads) * dim * 2 * 2, lambda: (
+            ops.norm_rotate_heads(v, dim, positions, cos=turn.cos, sin=turn.sin, interleaved=True),
+            ops.norm_rotate_heads(flat, dim, positions, cos=turn.cos, sin=turn.inverse_sin(), interleaved=True)))
+    ops.check_status("cuda")
+    out["kernels"] = kernels
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -1102,7 +1340,7 @@ def main():
     parser.add_argument("--kernel", default="both", choices=("both", "tcgen05", "mma"))
     parser.add_argument("--page-tokens", type=int, default=16, help="workloads: tokens per cache page")
     parser.add_argument("--max-context", type=int, default=0, help="workloads: the engine's context limit")
-    parser.add_argument("--design", choices=("mekazen", "zitezen"),
+    parser.add_argument("--design", choices=("mekazen", "zitezen", "sadosun"),
                         help="another decoder design beside Qwen3 at equal layer sizes, and its kernels beside their like")
     parser.add_argument("--chunk", type=int, default=0, help="--design: positions per chunk of the mask (0: the context)")
     parser.add_argument("--kernels-only", action="store_true",
@@ -1120,6 +1358,8 @@ def main():
         ops.set_decode_resident_blocks(args.decode_resident, max(args.decode_many, args.decode_resident))
     if args.design == "zitezen" and not args.workload:
         return design_zitezen(args)
+    if args.design == "sadosun" and not args.workload:
+        return design_sadosun(args)
     if args.design and not args.workload:
         return design(args)
     if args.workload:

@@ -931,7 +931,8 @@ __global__ void __launch_bounds__(256)
 paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                              const int* __restrict__ row_token, const int* __restrict__ positions,
                              int rows, int heads, int head_dim, int max_splits, int window, int chunk, int slots,
-                             const T* __restrict__ gate, long long gate_stride, int* status) {
+                             const T* __restrict__ gate, long long gate_stride, int has_sink, float sink_score,
+                             int* status) {
   chain_release();
   const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
   const int token = row_token[row];  // the step's integers are not written by any kernel of the step
@@ -978,6 +979,7 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
     }
     m = round_max;
   }
+  if (has_sink) l += expf(sink_score - m);   // one more key, without a value, in the denominator
   float value = acc / l;
   if (gate != nullptr) {
     // an output gate over the concatenated heads: value * sigmoid(g), written
@@ -1007,6 +1009,9 @@ struct DecodeProject {
   long long gate_stride = 0;
   // A cap on the scaled scores ahead of the softmax (0: none).
   float softcap = 0.0f;
+  // A key without a value that every query sees, with this score (has_sink 0: none).
+  int has_sink = 0;
+  float sink_score = 0.0f;
 };
 
 template <typename T, int HD, int G>
@@ -1035,7 +1040,8 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
   return static_cast<int>(launch_chained(paged_attention_merge_kernel<T>, dim3(rows, heads), dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0,
                                          stream, static_cast<const float*>(partial), static_cast<T*>(out),
                                          row_token, positions, rows, heads, HD, max_splits, window, chunk, 0,
-                                         static_cast<const T*>(project.gate), project.gate_stride, status));
+                                         static_cast<const T*>(project.gate), project.gate_stride, project.has_sink,
+                                         project.sink_score, status));
 }
 
 static int decode_resident_blocks = 444;   // blocks of the decode attention that fit the GPU at once (3 an SM); 0: always one block per tile
@@ -1054,12 +1060,14 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
                                                        positions, rows, project.tokens, heads, project.hidden,
                                                        max_splits, window, chunk, slots, kSplitKeys, kDecodeMinusHuge,
                                                        static_cast<const __nv_bfloat16*>(project.gate),
-                                                       project.gate_stride, status, stream));
+                                                       project.gate_stride, project.has_sink, project.sink_score,
+                                                       status, stream));
     return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
                                            dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream,
                                            static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out),
                                            row_token, positions, rows, heads, HD, max_splits, window, chunk, slots,
-                                           static_cast<const __nv_bfloat16*>(project.gate), project.gate_stride, status));
+                                           static_cast<const __nv_bfloat16*>(project.gate), project.gate_stride,
+                                           project.has_sink, project.sink_score, status));
   };
   static_assert(4 * 8 * (HD + 2) * sizeof(float) <= kSplitKeys * HD * 2, "the merge area must fit over the keys");
   dim3 grid(max_splits, kv_heads, rows);
@@ -1149,8 +1157,8 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
                                        const int* row_request, const int* positions, int rows,
                                        int heads, int kv_heads, int head_dim, int page_tokens,
                                        int num_pages, int max_splits, int window, int chunk, float scale,
-                                       int dtype, const void* gate, long long gate_stride, float softcap, int* status,
-                                       cudaStream_t stream) {
+                                       int dtype, const void* gate, long long gate_stride, float softcap, int has_sink,
+                                       float sink_score, int* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (!mxb_paged_attention_decode_supported(head_dim, heads, kv_heads, dtype) || max_splits <= 0)
     return static_cast<int>(cudaErrorInvalidValue);
@@ -1159,6 +1167,8 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
   project.gate = gate;
   project.gate_stride = gate_stride;
   project.softcap = softcap;
+  project.has_sink = has_sink;
+  project.sink_score = sink_score;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
              heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream, project
 #define BY_GROUP(T, HD)                                        \
@@ -1197,7 +1207,8 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
                                                int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
                                                int max_splits, int window, int chunk, float scale, const void* w, long long ldw,
                                                int hidden, float* summands, const void* gate, long long gate_stride,
-                                               float softcap, int* status, cudaStream_t stream) {
+                                               float softcap, int has_sink, float sink_score, int* status,
+                                               cudaStream_t stream) {
   if (rows <= 0 || hidden <= 0 || max_splits <= 0) return static_cast<int>(cudaErrorInvalidValue);
   if (!mxb_paged_attention_decode_project_supported(head_dim, heads, kv_heads, kBF16, tokens, w, ldw))
     return static_cast<int>(cudaErrorInvalidValue);
@@ -1210,6 +1221,8 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
   project.gate = gate;
   project.gate_stride = gate_stride;
   project.softcap = softcap;
+  project.has_sink = has_sink;
+  project.sink_score = sink_score;
   void* out = nullptr;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
              heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream, project
@@ -1281,7 +1294,7 @@ MXB_API int mxb_paged_attention_decode_noalloc(const void* q, const void* cache,
   if (e != cudaSuccess) return static_cast<int>(e);
   return mxb_paged_attention_decode(q, cache, out, scratch, block_tables, max_pages, row_token,
                                     row_request, positions, rows, heads, kv_heads, head_dim, page_tokens,
-                                    num_pages, splits, window, 0, scale, dtype, nullptr, 0, 0.0f, status, stream);
+                                    num_pages, splits, window, 0, scale, dtype, nullptr, 0, 0.0f, 0, 0.0f, status, stream);
 }
 
 MXB_TIMELINE_EXPORT(mxb_timeline_attention)

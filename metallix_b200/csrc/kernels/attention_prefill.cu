@@ -74,7 +74,8 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                      const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
                      int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale, float softcap,
-                     const __nv_bfloat16* __restrict__ gate, long long gate_stride, int* status) {
+                     const __nv_bfloat16* __restrict__ gate, long long gate_stride, int has_sink, float sink_log2,
+                     int* status) {
   constexpr int CHUNKS = HD / 8;                      // 16-byte chunks per row
   constexpr int TILE_BYTES = kFlashKeys * HD * 2;
   extern __shared__ __align__(128) unsigned char shared[];
@@ -273,6 +274,10 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     __syncthreads();  // this stage may be refilled by the next iteration's copies
   }
 
+  if (has_sink) {   // one more key, without a value, in the denominator (its score in units of log 2)
+    l_lo += fast_exp2(sink_log2 - m_lo);
+    l_hi += fast_exp2(sink_log2 - m_hi);
+  }
   const float inv_lo = valid_lo ? 1.0f / l_lo : 0.0f, inv_hi = valid_hi ? 1.0f / l_hi : 0.0f;
   __nv_bfloat16* out_lo = out + (static_cast<size_t>(t0 + row_lo) * heads + head) * HD;
   __nv_bfloat16* out_hi = out + (static_cast<size_t>(t0 + row_hi) * heads + head) * HD;
@@ -300,7 +305,7 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
                         const int* tile_request, const int* tile_start, const int* tile_length,
                         const int* positions, int tiles, int heads, int kv_heads, int page_tokens,
                         int num_pages, int window, int chunk, float scale, const void* gate, long long gate_stride,
-                        float softcap, int* status, cudaStream_t stream) {
+                        float softcap, int has_sink, float sink_score, int* status, cudaStream_t stream) {
   const int shared = 4 * kFlashKeys * HD * 2;
   auto kernel = flash_prefill_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
@@ -310,7 +315,7 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
       static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start, tile_length,
       positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, softcap,
-      static_cast<const __nv_bfloat16*>(gate), gate_stride, status);
+      static_cast<const __nv_bfloat16*>(gate), gate_stride, has_sink, sink_score * 1.4426950408889634f, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -333,14 +338,14 @@ MXB_API int mxb_flash_prefill(const void* q, const void* cache, void* out, const
                               const int* tile_length, const int* positions, int tiles, int heads,
                               int kv_heads, int head_dim, int page_tokens, int num_pages, int window, int chunk,
                               float scale, int dtype, const void* gate, long long gate_stride, float softcap,
-                              int* status, cudaStream_t stream) {
+                              int has_sink, float sink_score, int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (!mxb_flash_prefill_supported(head_dim, heads, kv_heads, dtype)) return static_cast<int>(cudaErrorInvalidValue);
   if (head_dim == 64)
     return launch_flash<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                            positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, softcap, status,
-                            stream);
+                            positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, softcap, has_sink,
+                            sink_score, status, stream);
   return launch_flash<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
-                           positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, softcap, status,
-                            stream);
+                           positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, softcap, has_sink,
+                            sink_score, status, stream);
 }

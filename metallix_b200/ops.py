@@ -58,21 +58,22 @@ _SIGNATURES = {
     "mxb_rotate_into": [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _I, _I, _P, _P],
     "mxb_relu_squared": [_P, _P, _L, _I, _P],
     "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                                   _F, _I, _P, _L, _F, _P, _P],
+                                   _F, _I, _P, _L, _F, _I, _F, _P, _P],
     "mxb_postnorm_add_rmsnorm": [_P, _P, _I, _I, _P, _F, _P, _I, _P, _F, _I, _I, _P],
     "mxb_sigmoid_gate": [_P, _P, _P, _L, _L, _L, _I, _I, _I, _P],
     "mxb_softcap": [_P, _F, _L, _P],
     "mxb_paged_attention_decode_supported": [_I, _I, _I, _I],
     "mxb_paged_attention_decode_project_supported": [_I, _I, _I, _I, _I, _P, _L],
     "mxb_paged_attention_decode_project": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                                           _F, _P, _L, _I, _P, _P, _L, _F, _P, _P],
+                                           _F, _P, _L, _I, _P, _P, _L, _F, _I, _F, _P, _P],
     "mxb_paged_attention_split_keys": [],
     "mxb_set_decode_resident_blocks": [_I, _I],
-    "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _L, _F, _P, _P],
+    "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _L, _F, _I, _F,
+                          _P, _P],
     "mxb_flash_prefill_supported": [_I, _I, _I, _I],
     "mxb_flash_prefill_tile": [],
     "mxb_flash_prefill_tcgen05": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P,
-                                  _P, _L, _F, _P, _P],
+                                  _P, _L, _F, _I, _F, _P, _P],
     "mxb_flash_prefill_tcgen05_supported": [_I, _I, _I, _I, _I],
     "mxb_flash_prefill_tcgen05_tile": [],
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
@@ -1010,7 +1011,7 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
                   tile_request: torch.Tensor, tile_start: torch.Tensor, tile_length: torch.Tensor,
                   positions: torch.Tensor, scale: float, window: int = 0, kernel: str = "auto",
                   longest_context: int = 0, chunk: int = 0, gate: Optional[torch.Tensor] = None,
-                  softcap: float = 0.0) -> torch.Tensor:
+                  softcap: float = 0.0, sink: Optional[float] = None) -> torch.Tensor:
     """Causal attention of prompt portions on the tensor cores (bfloat16,
     float32 softmax and accumulation); tiles hold up to 128 consecutive tokens
     of one request. ``kernel``: "tcgen05" (TMA, tensor memory), "mma" (the
@@ -1018,7 +1019,8 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
     ``longest_context`` (the most keys any of the tiles sees, 0: unknown)
     lets the tcgen05 kernel share a tile's keys out among several blocks when
     the tiles alone would leave most of the GPU idle. ``softcap`` c: scores
-    pass c tanh(s / c) ahead of the softmax."""
+    pass c tanh(s / c) ahead of the softmax. ``sink``: the score of one more
+    key that has no value and that every query sees."""
     _need(softcap >= 0.0, "the cap on the scores cannot be negative")
     _check(q, "q", (torch.bfloat16,), 3)
     _check(out, "out", (torch.bfloat16,), 3)
@@ -1055,7 +1057,8 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
               block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(),
               tile_length.data_ptr(), positions.data_ptr(), tokens, tiles, heads, kv_heads, head_dim,
               page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], shares, _ptr(partial),
-              _ptr(gate), gate_stride, float(softcap), status_word(q.device).data_ptr(), _stream())
+              _ptr(gate), gate_stride, float(softcap), 0 if sink is None else 1, float(sink or 0.0),
+              status_word(q.device).data_ptr(), _stream())
         if shares > 1:
             global _launches
             _launches += 1   # the kernel that puts the shares together
@@ -1064,7 +1067,7 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
           block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(), tile_length.data_ptr(),
           positions.data_ptr(), tiles, heads, kv_heads, head_dim, page_tokens, num_pages,
           int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], _ptr(gate), gate_stride, float(softcap),
-          status_word(q.device).data_ptr(), _stream())
+          0 if sink is None else 1, float(sink or 0.0), status_word(q.device).data_ptr(), _stream())
     return out
 
 
@@ -1095,7 +1098,8 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
                            row_request: torch.Tensor, positions: torch.Tensor, scale: float,
                            longest_context: int, window: int = 0,
                            partial: Optional[torch.Tensor] = None, chunk: int = 0,
-                           gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
+                           gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                           sink: Optional[float] = None) -> torch.Tensor:
     """Attention of single tokens over their requests' cached keys, split
     along the keys. ``row_token[i]`` is the token (row of q and out) of the
     i-th decoded request, negative for a padding row; ``row_request[i]`` its
@@ -1104,7 +1108,9 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
     rows * heads * splits * (head_dim + 2) values, allocated here if absent.
     ``gate`` ([tokens, heads * head_dim] in q's type, rows may be strided):
     the output is multiplied by sigmoid(gate) as it is written. ``softcap`` c:
-    scores pass c tanh(s / c) ahead of the softmax."""
+    scores pass c tanh(s / c) ahead of the softmax. ``sink``: the score of one
+    more key that has no value and that every query sees (it joins the
+    denominator where the splits are put together)."""
     dtype = q.dtype
     _need(softcap >= 0.0, "the cap on the scores cannot be negative")
     _check(q, "q", tuple(_CODES), 3)
@@ -1132,7 +1138,7 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
           int(window or 0), int(chunk or 0), float(scale), _CODES[dtype], _ptr(gate), gate_stride, float(softcap),
-          status_word(q.device).data_ptr(), _stream())
+          0 if sink is None else 1, float(sink or 0.0), status_word(q.device).data_ptr(), _stream())
     return out
 
 
@@ -1160,7 +1166,8 @@ def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_t
                                    row_token: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor,
                                    scale: float, longest_context: int, weight: torch.Tensor,
                                    window: int = 0, chunk: int = 0,
-                                   gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
+                                   gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
+                                   sink: Optional[float] = None) -> torch.Tensor:
     """``paged_attention_decode`` followed at once by the output projection
     ``weight`` ``[hidden, heads * head_dim]``, for steps of up to 64 tokens in
     bfloat16. Returns float32 ``[heads, tokens, hidden]``: the projection's sum
@@ -1188,7 +1195,7 @@ def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_t
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, tokens, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
           int(window or 0), int(chunk or 0), float(scale), weight.data_ptr(), weight.stride(0), hidden, summands.data_ptr(),
-          _ptr(gate), gate_stride, float(softcap),
+          _ptr(gate), gate_stride, float(softcap), 0 if sink is None else 1, float(sink or 0.0),
           status_word(q.device).data_ptr(), _stream())
     return summands
 

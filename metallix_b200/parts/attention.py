@@ -158,19 +158,20 @@ def attend_cached(q_heads: torch.Tensor, cache: CacheView, ctx: StepContext, *, 
         return ops.paged_attention_decode_project(
             q_heads, cache.pool, cache.block_tables, tiles["decode_token"], tiles["decode_request"],
             ctx.positions, scale, tiles["longest_context"], project.weight, window, chunk, gate=gate,
-            softcap=softcap), True
+            softcap=softcap, sink=sink), True
     out = torch.empty_like(q_heads)
     if split:
         # Requests that bring one token: split along the keys.
         ops.paged_attention_decode(q_heads, cache.pool, out, cache.block_tables, tiles["decode_token"],
                                    tiles["decode_request"], ctx.positions, scale, tiles["longest_context"], window,
-                                   chunk=chunk, gate=gate, softcap=softcap)
+                                   chunk=chunk, gate=gate, softcap=softcap, sink=sink)
     if flash:
         # Requests that bring several tokens: tensor cores, tiles of 128.
         if tiles["wide_request"].numel():
             ops.flash_prefill(q_heads, cache.pool, out, cache.block_tables, tiles["wide_request"],
                               tiles["wide_start"], tiles["wide_length"], ctx.positions, scale, window,
-                              longest_context=tiles["longest_keys"], chunk=chunk, gate=gate, softcap=softcap)
+                              longest_context=tiles["longest_keys"], chunk=chunk, gate=gate, softcap=softcap,
+                              sink=sink)
         rest = None if split else slice(multi_tiles, None)   # single tokens not yet served
     else:
         rest = slice(0, multi_tiles) if split else slice(0, None)
@@ -259,7 +260,7 @@ class GQAttention:
         position_fuses = self.position is None or getattr(self.position, "fused_tables", False)
         self.dtype = runtime.dtype
         # What only the general kernel does: values of another width than the keys.
-        self.general_only = self.value_dim != self.head_dim or self.sink is not None
+        self.general_only = self.value_dim != self.head_dim
         self.fused = norms_fuse and eps_agree and position_fuses and self.value_dim == self.head_dim
         self.split_decode = not self.general_only and ops.decode_attention_supported(
             self.head_dim, self.num_heads, self.num_kv_heads, self.dtype)
