@@ -1152,15 +1152,6 @@ def design_sadosun(args):
     def weights_of(shapes):
         return WeightStore({name: (normal(*shape) * 0.02).to(bf16) for name, shape in shapes.items()})
 
-    def sink_attention(q, cache, out, table, tile_request, tile_start, tile_length, positions, longest):
-        """The kernel this design's attention part runs: a window, one more in the softmax's denominator."""
-        return ops.paged_attention_tile(q, cache, out, table, tile_request, tile_start, tile_length, positions,
-                                        dim ** -0.5, window, sink=0.0)
-
-    def prompt_tiles(tokens, tile=16):
-        starts = list(range(0, tokens, tile))
-        return ints([0] * len(starts)), ints(starts), ints([min(tile, tokens - s) for s in starts])
-
     # ---- what a sublayer reads: the sum, the norm, and (this design) the convolution over time
     for tokens in (8, prompt * 4):
         x, delta, ones = normal(tokens, hidden), normal(tokens, hidden).to(bf16), torch.ones(hidden, device="cuda")
@@ -1208,6 +1199,10 @@ def design_sadosun(args):
                 "sadosun: router, choice, %d distinct experts of %d" % (distinct, count): gbs(
                     distinct * 2 * ff * hidden * 2 + (count + identity) * hidden * 2, lambda: routed.forward(h, None)),
                 "qwen3: gate, up, activation, down": gbs(3 * inter * hidden * 2, lambda: dense.forward(h, None))}
+            few, routed.ROUTED_TOKENS = routed.ROUTED_TOKENS, 0 if tokens <= routed.ROUTED_TOKENS else 1 << 30
+            kernels[label]["sadosun: the same, the other way through the experts"] = gbs(
+                distinct * 2 * ff * hidden * 2 + (count + identity) * hidden * 2, lambda: routed.forward(h, None))
+            routed.ROUTED_TOKENS = few
         else:               # a prompt: the products that must be made
             kernels[label] = {
                 "sadosun: router, choice, the chosen experts": tflops(
@@ -1254,8 +1249,10 @@ def design_sadosun(args):
     kernels["decode_step_mixer_8_requests"]["qwen3: split-key attention over %d cached positions" % context] = gbs(
         kv_bytes, lambda: ops.paged_attention_decode(q, cache, attended, table, rows, rows, positions, dim ** -0.5,
                                                      context))
-    kernels["decode_step_mixer_8_requests"]["sadosun: attention with a sink over the same rows"] = gbs(
-        kv_bytes, lambda: sink_attention(q, cache, attended, table, rows, rows, one_each, positions, context))
+    kernels["decode_step_mixer_8_requests"]["sadosun: the same with a sink and a window of %d" % window] = gbs(
+        kv_bytes * min(window or context, context) // context,
+        lambda: ops.paged_attention_decode(q, cache, attended, table, rows, rows, positions, dim ** -0.5, context,
+                                           window, sink=0.0))
 
     # ---- a prompt in one step
     tokens = prompt
@@ -1286,8 +1283,11 @@ def design_sadosun(args):
     kernels[f"prompt_mixer_{tokens}"]["qwen3: tensor-core attention"] = tflops(
         flops, lambda: ops.flash_prefill(q, cache, attended, table, *tiles, positions, dim ** -0.5,
                                          longest_context=tokens))
-    kernels[f"prompt_mixer_{tokens}"]["sadosun: attention with a sink"] = tflops(
-        flops, lambda: sink_attention(q, cache, attended, table, *prompt_tiles(tokens), positions, tokens))
+    seen = min(window or tokens, tokens)       # keys a late query sees
+    kernels[f"prompt_mixer_{tokens}"]["sadosun: the same with a sink and a window of %d" % window] = tflops(
+        flops if seen == tokens else 4.0 * dim * heads * (seen * (seen + 1) / 2 + (tokens - seen) * seen),
+        lambda: ops.flash_prefill(q, cache, attended, table, *tiles, positions, dim ** -0.5, window,
+                                  longest_context=tokens, sink=0.0))
     v = normal(tokens, kv_heads * dim).to(bf16)
     turn = build_part("position", PartSpec("rope_interleaved", {"theta": 1.0e4, "rotary_dim": dim, "head_dim": dim,
                                                                "scaling": None}), WeightStore({}), runtime)

@@ -22,7 +22,7 @@ constexpr int kTcM = 128;     // rows of a tile
 constexpr int kTcK = 64;      // k per stage: 64 bfloat16 = one 128-byte swizzle row
 constexpr int kTcThreads = 192;
 
-enum TcEpilogue : int { kTcStoreBf16 = 0, kTcStoreF32 = 1, kTcSwiGLU = 2 };
+enum TcEpilogue : int { kTcStoreBf16 = 0, kTcStoreF32 = 1, kTcSwiGLU = 2, kTcReluSquared = 3 };
 
 template <int BN, int STAGES_> struct TcConfig {
   static constexpr int kStageBytes = (kTcM + BN) * kTcK * 2;
@@ -38,10 +38,18 @@ template <int BN, int STAGES_> struct TcConfig {
 // runs while the MMAs of the next fill the other accumulator and the TMA
 // loads run ahead of both. Tiles are numbered with the row tile fastest:
 // blocks working side by side share a tile of W.
+//
+// Grouped form (tile_group given): W holds several matrices of group_rows
+// rows each, one below the other, and row tile i of A is multiplied by matrix
+// tile_group[i]; a row tile whose entry is negative is left out by every warp
+// alike. The rows of A are then tokens sorted by the expert they go to, each
+// expert's rows padded to whole tiles. kTcReluSquared stores max(c, 0)^2 in
+// bfloat16.
 template <int BN, int EPI, int STAGES_>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    void* __restrict__ out, int m, int n, int k, long long ldo, int* status) {
+                    void* __restrict__ out, int m, int n, int k, long long ldo, const int* __restrict__ tile_group,
+                    int group_rows, int* status) {
   using Config = TcConfig<BN, STAGES_>;
   constexpr int STAGES = Config::kStages;
   constexpr int OUT_COLUMNS = EPI == kTcSwiGLU ? BN / 2 : BN;  // output columns of a tile
@@ -87,7 +95,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       int step = 0;  // k blocks issued so far, over all tiles
       for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * kTcM, n0 = (tile / m_tiles) * OUT_COLUMNS;
+        const int m0 = (tile % m_tiles) * kTcM;
+        int n0 = (tile / m_tiles) * OUT_COLUMNS;
+        if (tile_group != nullptr) {
+          const int group = tile_group[tile % m_tiles];
+          if (group < 0) continue;
+          n0 += group * group_rows;   // the rows of this group's matrix
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++step) {
           const int stage = step % STAGES;
           const uint32_t parity = (step / STAGES) & 1;
@@ -110,7 +124,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       constexpr uint32_t idesc = tc_instruction_descriptor(kTcM, BN);
       int step = 0, local = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
+      for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+        if (tile_group != nullptr && tile_group[tile % m_tiles] < 0) continue;
         const int buffer = local & 1;
         // The epilogue must have drained this accumulator (two tiles ago).
         if (!barrier_wait(&accumulator_empty[buffer], ((local >> 1) & 1) ^ 1, status)) { failed = 1; break; }
@@ -131,13 +146,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           tc_commit(&empty_barrier[stage]);
         }
         tc_commit(&accumulator_full[buffer]);  // arrives when this tile's accumulator is final
+        ++local;
       }
     }
   } else {
     // ---- epilogue: warp w reads the 32 accumulator rows (lanes) (w % 4) * 32 ...
     const int lane_base = (warp & 3) * 32;
     int local = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      if (tile_group != nullptr && tile_group[tile % m_tiles] < 0) continue;
       const int buffer = local & 1;
       const int m0 = (tile % m_tiles) * kTcM, n0 = (tile / m_tiles) * OUT_COLUMNS;
       if (!barrier_wait(&accumulator_full[buffer], (local >> 1) & 1, status)) { failed = 1; break; }
@@ -159,6 +176,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const float gate = to_float(from_float<__nv_bfloat16>(__uint_as_float(acc[i])));
             const float u = to_float(from_float<__nv_bfloat16>(__uint_as_float(up[i])));
             values[i] = __fdividef(gate, 1.0f + __expf(-gate)) * u;  // the result is rounded to bfloat16 anyway
+          }
+        } else if (EPI == kTcReluSquared) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float u = fmaxf(__uint_as_float(acc[i]), 0.0f);
+            values[i] = u * u;
           }
         } else {
 #pragma unroll
@@ -199,6 +222,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // This thread has read all it needs of the accumulator: hand it back.
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
       barrier_arrive(&accumulator_empty[buffer]);
+      ++local;
     }
   }
 
@@ -220,7 +244,7 @@ int g_tc_bn = 0, g_tc_deep = -1;  // tuning overrides: tile width, deep (1) or s
 
 template <int BN, int EPI, int STAGES_>
 static int launch_tc_staged(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n, int k,
-                            long long ldo, int* status, cudaStream_t stream) {
+                            long long ldo, const int* tile_group, int group_rows, int* status, cudaStream_t stream) {
   using Config = TcConfig<BN, STAGES_>;
   auto kernel = gemm_tcgen05_kernel<BN, EPI, STAGES_>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSharedBytes);
@@ -234,7 +258,8 @@ static int launch_tc_staged(const CUtensorMap& map_a, const CUtensorMap& map_b, 
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
   }
   dim3 grid(tiles < sm_count ? tiles : sm_count);  // one block per SM walks over the tiles
-  kernel<<<grid, kTcThreads, Config::kSharedBytes, stream>>>(map_a, map_b, out, m, n, k, ldo, status);
+  kernel<<<grid, kTcThreads, Config::kSharedBytes, stream>>>(map_a, map_b, out, m, n, k, ldo, tile_group, group_rows,
+                                                             status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -242,11 +267,13 @@ static int launch_tc_staged(const CUtensorMap& map_a, const CUtensorMap& map_b, 
 // and tensor memory holds two accumulators). Shallow: half the stages.
 template <int BN, int EPI>
 static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_b, void* out, int m, int n, int k,
-                     long long ldo, int* status, cudaStream_t stream) {
+                     long long ldo, int* status, cudaStream_t stream, const int* tile_group = nullptr,
+                     int group_rows = 0) {
   constexpr int deep = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
   const bool shallow = g_tc_deep == 0;
-  if (shallow) return launch_tc_staged<BN, EPI, deep / 2>(map_a, map_b, out, m, n, k, ldo, status, stream);
-  return launch_tc_staged<BN, EPI, deep>(map_a, map_b, out, m, n, k, ldo, status, stream);
+  if (shallow)
+    return launch_tc_staged<BN, EPI, deep / 2>(map_a, map_b, out, m, n, k, ldo, tile_group, group_rows, status, stream);
+  return launch_tc_staged<BN, EPI, deep>(map_a, map_b, out, m, n, k, ldo, tile_group, group_rows, status, stream);
 }
 
 }  // namespace mxb
@@ -298,6 +325,35 @@ MXB_API int mxb_gemm_tcgen05(void* out, const void* a, const void* w, int m, int
   if (bn == 256) return launch_tc<256, kTcStoreBf16>(map_a, map_b, out, m, n, k, ldo, status, stream);
   if (bn == 128) return launch_tc<128, kTcStoreBf16>(map_a, map_b, out, m, n, k, ldo, status, stream);
   return launch_tc<64, kTcStoreBf16>(map_a, map_b, out, m, n, k, ldo, status, stream);
+}
+
+// The grouped product: a is [m, k], its rows sorted by group and each group's
+// rows padded to whole tiles of 128; w is [groups * group_rows, k], one
+// [group_rows, k] matrix per group; row tile i of a meets matrix
+// tile_group[i] (device memory, m / 128 rounded up entries; negative: the
+// tile is left out); out is [m, n] with n <= group_rows. epilogue: 1 float32,
+// 3 bfloat16 max(c, 0)^2, 0 bfloat16.
+MXB_API int mxb_gemm_tcgen05_grouped(void* out, const void* a, const void* w, const int* tile_group, int m, int n,
+                                     int k, int groups, int group_rows, long long lda, long long ldw, long long ldo,
+                                     int epilogue, int* status, cudaStream_t stream) {
+  if (!mxb_gemm_tcgen05_supported(m, n, k, lda, ldw) || groups < 1 || n > group_rows || tile_group == nullptr)
+    return static_cast<int>(cudaErrorInvalidValue);
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return static_cast<int>(cudaErrorInvalidValue);
+  const long long w_rows = static_cast<long long>(groups) * group_rows;
+  if (w_rows > 0x7fffffffLL) return static_cast<int>(cudaErrorInvalidValue);
+  const int bn = n > 128 ? 256 : (n > 64 ? 128 : 64);
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, a, m, k, lda, kTcM) || !make_map(&map_b, w, static_cast<int>(w_rows), k, ldw, bn))
+    return static_cast<int>(cudaErrorInvalidValue);
+#define GROUPED(EPI)                                                                                             \
+  if (bn == 256) return launch_tc<256, EPI>(map_a, map_b, out, m, n, k, ldo, status, stream, tile_group, group_rows); \
+  if (bn == 128) return launch_tc<128, EPI>(map_a, map_b, out, m, n, k, ldo, status, stream, tile_group, group_rows); \
+  return launch_tc<64, EPI>(map_a, map_b, out, m, n, k, ldo, status, stream, tile_group, group_rows);
+  if (epilogue == kTcStoreF32) { GROUPED(kTcStoreF32) }
+  if (epilogue == kTcReluSquared) { GROUPED(kTcReluSquared) }
+  if (epilogue == kTcStoreBf16) { GROUPED(kTcStoreBf16) }
+#undef GROUPED
+  return static_cast<int>(cudaErrorInvalidValue);
 }
 
 // Tuning hook: force the tile width (64, 128, 256; 0 = choose) and the

@@ -12,16 +12,21 @@
 // of weights over the real experts (zeros for those not chosen) and the sum of
 // the weights that fell on identity experts.
 //
-// Two ways through the experts W_down act(W_up h), act(u) = relu(u)^2:
-// * all experts at once, for steps of many tokens: one product with the
-//   stacked W_up [experts * ff, hidden], dense_act_kernel squares, and
-//   multiplies column e * ff + f by the token's weight for expert e (zero for
-//   most), one product with W_down [hidden, experts * ff];
-// * only the chosen ones, for steps of few tokens: routed_up_kernel (a warp
-//   per row of a chosen expert's W_up) and routed_down_kernel (a warp per
-//   output value, over the chosen experts' column blocks of W_down), so that
-//   a decode step reads `top` experts' weights and not all of them.
-// Both add weight_identity * h at the end (add_identity_kernel, or inside
+// Two ways through the experts W_down act(W_up h), act(u) = relu(u)^2, with
+// W_up stacked [experts * ff, hidden] and W_down stacked [experts * hidden, ff]:
+// * grouped, for steps of many tokens: expert_rows_kernel gives every
+//   (token, choice) pair a row in an array sorted by expert, each expert's
+//   rows padded to whole tiles of kGroupTile, and names each tile's expert;
+//   gather_rows_kernel copies the tokens' inputs there; two grouped
+//   tensor-core products (the first with relu^2 in its epilogue) run each
+//   tile against its expert's matrices; combine_rows_kernel sums a token's
+//   rows with their weights. Every pair costs one row of each product, so
+//   the work is `top` experts per token however many experts there are.
+// * row by row, for steps of few tokens and for float32: routed_up_kernel (a
+//   warp per row of a chosen expert's W_up) and routed_down_kernel (a warp
+//   per output value, over the chosen experts' W_down), so that a decode step
+//   reads `top` experts' weights and not all of them.
+// Both add weight_identity * h at the end (combine_rows_kernel, or inside
 // routed_down_kernel).
 #include "common.cuh"
 
@@ -94,21 +99,6 @@ route_kernel(const float* __restrict__ logits, const float* __restrict__ correct
   }
 }
 
-// act[t, e * ff + f] = relu(up[t, e * ff + f])^2 * dense[t, e]
-template <typename T>
-__global__ void dense_act_kernel(const T* __restrict__ up, const float* __restrict__ dense, T* __restrict__ act,
-                                 long long total, int experts, int ff) {
-  const long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (index >= total) return;
-  const long long width = static_cast<long long>(experts) * ff;
-  const long long t = index / width;
-  const int e = static_cast<int>((index - t * width) / ff);
-  const float w = dense[t * experts + e];
-  float u = w != 0.0f ? to_float(up[index]) : 0.0f;
-  u = fmaxf(u, 0.0f);
-  act[index] = from_float<T>(u * u * w);
-}
-
 // y[t, :] += identity_weight[t] * h[t, :]   (y float32)
 template <typename T>
 __global__ void add_identity_kernel(float* __restrict__ y, const T* __restrict__ h,
@@ -117,6 +107,114 @@ __global__ void add_identity_kernel(float* __restrict__ y, const T* __restrict__
   if (index >= total) return;
   const float w = identity_weight[index / hidden];
   if (w != 0.0f) y[index] = fmaf(w, to_float(h[index]), y[index]);
+}
+
+constexpr int kGroupTile = 128;      // rows of a tile of the grouped products
+constexpr int kGroupThreads = 1024;
+constexpr int kGroupExperts = 1024;  // the most experts expert_rows_kernel counts in shared memory
+
+// One block. position[p] = the row of pair p = (token, choice) in the array
+// sorted by expert (-1 for an identity expert); tile_group[i] = the expert of
+// row tile i (-1 for the tiles that stay empty). Expert e's rows start at the
+// sum of the experts' before it, each rounded up to whole tiles. Which of an
+// expert's rows a pair gets depends on the order the threads arrive in; the
+// products treat every row alike, so the result does not.
+__global__ void __launch_bounds__(kGroupThreads)
+expert_rows_kernel(const int* __restrict__ chosen, int* __restrict__ position, int* __restrict__ tile_group,
+                   int pairs, int experts, int tiles) {
+  __shared__ int count[kGroupExperts], start[kGroupExperts], cursor[kGroupExperts];
+  __shared__ int used_tiles;
+  for (int e = threadIdx.x; e < experts; e += kGroupThreads) { count[e] = 0; cursor[e] = 0; }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += kGroupThreads) {
+    const int e = chosen[p];
+    if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tile = 0;
+    for (int e = 0; e < experts; ++e) {
+      start[e] = tile;
+      tile += (count[e] + kGroupTile - 1) / kGroupTile;
+    }
+    used_tiles = tile;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += kGroupThreads) {
+    const int first = start[e], last = first + (count[e] + kGroupTile - 1) / kGroupTile;
+    for (int tile = first; tile < last && tile < tiles; ++tile) tile_group[tile] = e;
+  }
+  for (int tile = used_tiles + threadIdx.x; tile < tiles; tile += kGroupThreads) tile_group[tile] = -1;
+  for (int p = threadIdx.x; p < pairs; p += kGroupThreads) {
+    const int e = chosen[p];
+    position[p] = e >= 0 && e < experts ? start[e] * kGroupTile + atomicAdd(&cursor[e], 1) : -1;
+  }
+}
+
+// sorted[position[p], :] = h[p / top, :], 16 bytes a thread at a time (hidden * sizeof(T) a multiple of 16)
+template <typename T>
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const T* __restrict__ h, const int* __restrict__ position, T* __restrict__ sorted, int pairs,
+                   int hidden, int top) {
+  const int p = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (p >= pairs) return;
+  const int row = position[p];
+  if (row < 0) return;
+  const uint4* src = reinterpret_cast<const uint4*>(h + static_cast<size_t>(p / top) * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(sorted + static_cast<size_t>(row) * hidden);
+  const int vectors = hidden * static_cast<int>(sizeof(T)) / 16;
+  for (int i = lane; i < vectors; i += 32) dst[i] = src[i];
+}
+
+// y[t, c] = sum_k weights[t, k] * rows[position[t, k], c] + identity_weight[t] * h[t, c]; four columns a thread
+template <typename T>
+__global__ void __launch_bounds__(256)
+combine_rows_kernel(const float* __restrict__ rows, const int* __restrict__ position,
+                    const float* __restrict__ weights, const float* __restrict__ identity_weight,
+                    const T* __restrict__ h, float* __restrict__ y, int hidden, int top) {
+  const int t = blockIdx.x;
+  const float on_identity = identity_weight[t];
+  for (int c = threadIdx.x * 4; c < hidden; c += 256 * 4) {
+    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int k = 0; k < top; ++k) {
+      const int row = position[static_cast<size_t>(t) * top + k];
+      if (row < 0) continue;
+      const float w = weights[static_cast<size_t>(t) * top + k];
+      const float4 v = *reinterpret_cast<const float4*>(rows + static_cast<size_t>(row) * hidden + c);
+      sum[0] = fmaf(w, v.x, sum[0]); sum[1] = fmaf(w, v.y, sum[1]);
+      sum[2] = fmaf(w, v.z, sum[2]); sum[3] = fmaf(w, v.w, sum[3]);
+    }
+    if (on_identity != 0.0f) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sum[i] = fmaf(on_identity, to_float(h[static_cast<size_t>(t) * hidden + c + i]), sum[i]);
+    }
+    *reinterpret_cast<float4*>(y + static_cast<size_t>(t) * hidden + c) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+  }
+}
+
+// A lane's share of the dot product of a weight row with a vector: 16 bytes
+// of the row at a time where the row starts on such a boundary and its length
+// allows it, one value at a time otherwise.
+template <typename T, typename U>
+__device__ __forceinline__ float dot_rows(const T* __restrict__ row, const U* __restrict__ x, int length, int lane) {
+  constexpr int V = 16 / static_cast<int>(sizeof(T));
+  float sum = 0.0f;
+  if (length % V == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};     // independent chains: the loads of a row are all in flight
+    int lap = 0;
+    for (int i = lane * V; i < length; i += 32 * V, ++lap) {
+      const uint4 q = *reinterpret_cast<const uint4*>(row + i);
+      const T* w = reinterpret_cast<const T*>(&q);
+      float s = 0.0f;
+#pragma unroll
+      for (int v = 0; v < V; ++v) s = fmaf(to_float(w[v]), to_float(x[i + v]), s);
+      partial[lap & 3] += s;
+    }
+    sum = (partial[0] + partial[1]) + (partial[2] + partial[3]);
+  } else {
+    for (int i = lane; i < length; i += 32) sum = fmaf(to_float(row[i]), to_float(x[i]), sum);
+  }
+  return sum;
 }
 
 constexpr int kRoutedThreads = 256;   // eight warps, a row of a weight each
@@ -133,8 +231,7 @@ routed_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int*
   if (f >= ff || e >= experts || e < 0) return;
   const T* x = h + static_cast<size_t>(pair / top) * hidden;
   const T* row = w_up + (static_cast<size_t>(e) * ff + f) * hidden;
-  float sum = 0.0f;
-  for (int i = lane; i < hidden; i += 32) sum = fmaf(to_float(row[i]), to_float(x[i]), sum);
+  float sum = dot_rows(row, x, hidden, lane);
   sum = warp_sum(sum);
   if (lane == 0) {
     const float u = fmaxf(sum, 0.0f);
@@ -142,7 +239,7 @@ routed_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int*
   }
 }
 
-// y[t, c] = sum_k W_down[c, e_k * ff : (e_k + 1) * ff] . act[(t, k), :]  +  (sum of identity weights) * h[t, c]
+// y[t, c] = sum_k W_down[e_k * hidden + c, :] . act[(t, k), :]  +  (sum of identity weights) * h[t, c]
 template <typename T>
 __global__ void __launch_bounds__(kRoutedThreads)
 routed_down_kernel(const float* __restrict__ act, const T* __restrict__ w_down, const T* __restrict__ h,
@@ -152,7 +249,6 @@ routed_down_kernel(const float* __restrict__ act, const T* __restrict__ w_down, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.y * (kRoutedThreads / 32) + warp;
   if (c >= hidden) return;
-  const size_t width = static_cast<size_t>(experts) * ff;
   float sum = 0.0f, on_identity = 0.0f;
   for (int k = 0; k < top; ++k) {
     const int e = chosen[static_cast<size_t>(t) * top + k];
@@ -161,9 +257,9 @@ routed_down_kernel(const float* __restrict__ act, const T* __restrict__ w_down, 
       on_identity += weights[static_cast<size_t>(t) * top + k];
       continue;
     }
-    const T* row = w_down + static_cast<size_t>(c) * width + static_cast<size_t>(e) * ff;
+    const T* row = w_down + (static_cast<size_t>(e) * hidden + c) * ff;
     const float* a = act + (static_cast<size_t>(t) * top + k) * ff;
-    for (int i = lane; i < ff; i += 32) sum = fmaf(to_float(row[i]), a[i], sum);
+    sum += dot_rows(row, a, ff, lane);
   }
   sum = warp_sum(sum);
   if (lane == 0) y[static_cast<size_t>(t) * hidden + c] = fmaf(on_identity, to_float(h[static_cast<size_t>(t) * hidden + c]), sum);
@@ -188,22 +284,6 @@ MXB_API int mxb_route_experts(const float* logits, const float* correction, int*
   return static_cast<int>(cudaGetLastError());
 }
 
-MXB_API int mxb_experts_dense_act(const void* up, const float* dense, void* act, int tokens, int experts, int ff,
-                                  int dtype, cudaStream_t stream) {
-  const long long total = static_cast<long long>(tokens) * experts * ff;
-  if (total <= 0) return 0;
-  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
-  if (dtype == kF32)
-    dense_act_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(up), dense,
-                                                       static_cast<float*>(act), total, experts, ff);
-  else if (dtype == kBF16)
-    dense_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(up), dense,
-                                                               static_cast<__nv_bfloat16*>(act), total, experts, ff);
-  else
-    return static_cast<int>(cudaErrorInvalidValue);
-  return static_cast<int>(cudaGetLastError());
-}
-
 MXB_API int mxb_experts_add_identity(float* y, const void* h, const float* identity_weight, int tokens, int hidden,
                                      int dtype, cudaStream_t stream) {
   const long long total = static_cast<long long>(tokens) * hidden;
@@ -219,7 +299,7 @@ MXB_API int mxb_experts_add_identity(float* y, const void* h, const float* ident
   return static_cast<int>(cudaGetLastError());
 }
 
-// h: [tokens, hidden]; w_up: [experts * ff, hidden]; w_down: [hidden, experts * ff]; act: float32 scratch
+// h: [tokens, hidden]; w_up: [experts * ff, hidden]; w_down: [experts * hidden, ff]; act: float32 scratch
 // [tokens * top, ff]; y: float32 [tokens, hidden].
 MXB_API int mxb_experts_routed(const void* h, const void* w_up, const void* w_down, const int* chosen,
                                const float* weights, float* act, float* y, int tokens, int hidden, int experts, int ff,
@@ -243,5 +323,60 @@ MXB_API int mxb_experts_routed(const void* h, const void* w_up, const void* w_do
   } else {
     return static_cast<int>(cudaErrorInvalidValue);
   }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The rows of a tile of the grouped products, and the most experts mxb_expert_rows takes.
+MXB_API int mxb_expert_rows_tile() { return kGroupTile; }
+MXB_API int mxb_expert_rows_experts() { return kGroupExperts; }
+
+// chosen: int32 [pairs]; position: int32 [pairs]; tile_group: int32 [tiles], tiles >= (pairs + experts *
+// (tile - 1)) / tile rounded up, which holds every expert's rows however they fall.
+MXB_API int mxb_expert_rows(const int* chosen, int* position, int* tile_group, int pairs, int experts, int tiles,
+                            cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  if (experts < 1 || experts > kGroupExperts ||
+      static_cast<long long>(tiles) * kGroupTile < static_cast<long long>(pairs) + static_cast<long long>(experts) * (kGroupTile - 1))
+    return static_cast<int>(cudaErrorInvalidValue);
+  expert_rows_kernel<<<1, kGroupThreads, 0, stream>>>(chosen, position, tile_group, pairs, experts, tiles);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// sorted[position[p], :] = h[p / top, :] for the pairs with a position; hidden * the element's size a multiple of 16.
+MXB_API int mxb_expert_gather_rows(const void* h, const int* position, void* sorted, int pairs, int hidden, int top,
+                                   int dtype, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  const int size = dtype == kF32 ? 4 : 2;
+  if (hidden <= 0 || top <= 0 || (hidden * size) % 16 != 0 || (reinterpret_cast<uintptr_t>(h) & 15) ||
+      (reinterpret_cast<uintptr_t>(sorted) & 15))
+    return static_cast<int>(cudaErrorInvalidValue);
+  const unsigned blocks = static_cast<unsigned>(ceil_div(pairs, 8));
+  if (dtype == kF32)
+    gather_rows_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(h), position,
+                                                         static_cast<float*>(sorted), pairs, hidden, top);
+  else if (dtype == kBF16)
+    gather_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(h), position,
+                                                                 static_cast<__nv_bfloat16*>(sorted), pairs, hidden, top);
+  else
+    return static_cast<int>(cudaErrorInvalidValue);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// rows: float32 [sorted rows, hidden]; y: float32 [tokens, hidden]; hidden a multiple of 4.
+MXB_API int mxb_expert_combine_rows(const float* rows, const int* position, const float* weights,
+                                    const float* identity_weight, const void* h, float* y, int tokens, int hidden,
+                                    int top, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden <= 0 || hidden % 4 != 0 || top <= 0 || (reinterpret_cast<uintptr_t>(rows) & 15) ||
+      (reinterpret_cast<uintptr_t>(y) & 15))
+    return static_cast<int>(cudaErrorInvalidValue);
+  if (dtype == kF32)
+    combine_rows_kernel<float><<<tokens, 256, 0, stream>>>(rows, position, weights, identity_weight,
+                                                          static_cast<const float*>(h), y, hidden, top);
+  else if (dtype == kBF16)
+    combine_rows_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>(rows, position, weights, identity_weight,
+                                                                  static_cast<const __nv_bfloat16*>(h), y, hidden, top);
+  else
+    return static_cast<int>(cudaErrorInvalidValue);
   return static_cast<int>(cudaGetLastError());
 }

@@ -53,27 +53,58 @@ selective_scan_kernel(const T* __restrict__ x, long long ldx, const float* __res
     decay[j] = k < states ? a[static_cast<size_t>(cc) * states + k] : 0.0f;
   }
   const float bias = step_bias[cc], skip = d[cc];
-  for (int i = 0; i < n; ++i) {
-    const size_t t = static_cast<size_t>(start + i);
-    const float dt = softplus_of(step[t * ld_step + cc] + bias);
-    const float xv = to_float(x[t * ldx + cc]);
-    const float dx = dt * xv;
-    const T* bt = b + t * ldbc;
-    const T* ct = c + t * ldbc;
-    float y = 0.0f;
+  // The recurrence ties a token to the one before it only through one
+  // multiply-add per state; everything else about a token (its loads, step
+  // size, decays, increments, gate) does not wait for the token before. So
+  // AHEAD tokens are fetched and prepared side by side, then stepped through.
+  // A token past the row's end repeats the last one's loads with a decay of
+  // one and an increment of zero, which leaves the state as it is.
+  constexpr int AHEAD = PER <= 4 ? 8 : (PER <= 16 ? 2 : 1);
+  for (int i0 = 0; i0 < n; i0 += AHEAD) {
+    float pv[AHEAD], xs[AHEAD], zs[AHEAD];
+    T bs[AHEAD][PER], cs[AHEAD][PER];
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      const int k = lane + kScanLanes * j;
-      if (k < states) {
-        s[j] = fmaf(expf(dt * decay[j]), s[j], dx * to_float(bt[k]));
-        y = fmaf(s[j], to_float(ct[k]), y);
+    for (int u = 0; u < AHEAD; ++u) {
+      const size_t t = static_cast<size_t>(start + (i0 + u < n ? i0 + u : n - 1));
+      pv[u] = step[t * ld_step + cc];
+      xs[u] = to_float(x[t * ldx + cc]);
+      zs[u] = to_float(z[t * ldz + cc]);
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int k = lane + kScanLanes * j;
+        bs[u][j] = k < states ? b[t * ldbc + k] : from_float<T>(0.0f);   // a state that is not there stays at zero
+        cs[u][j] = k < states ? c[t * ldbc + k] : from_float<T>(0.0f);
       }
     }
-    y += __shfl_xor_sync(0xffffffffu, y, 1);
-    y += __shfl_xor_sync(0xffffffffu, y, 2);
-    if (lane == 0 && live) {
-      const float zv = to_float(z[t * ldz + cc]);
-      out[t * channels + cc] = from_float<T>(fmaf(skip, xv, y) * (zv / (1.0f + expf(-zv))));
+    float keep[AHEAD][PER], add[AHEAD][PER], gate[AHEAD], y[AHEAD];
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+      const bool valid = i0 + u < n;
+      const float dt = softplus_of(pv[u] + bias);
+      const float dx = dt * xs[u];
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        keep[u][j] = valid ? expf(dt * decay[j]) : 1.0f;
+        add[u][j] = valid ? dx * to_float(bs[u][j]) : 0.0f;
+      }
+      gate[u] = zs[u] / (1.0f + expf(-zs[u]));
+    }
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        s[j] = fmaf(keep[u][j], s[j], add[u][j]);
+        sum = fmaf(s[j], to_float(cs[u][j]), sum);
+      }
+      y[u] = sum;
+    }
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+      y[u] += __shfl_xor_sync(0xffffffffu, y[u], 1);
+      y[u] += __shfl_xor_sync(0xffffffffu, y[u], 2);
+      if (lane == 0 && live && i0 + u < n)
+        out[static_cast<size_t>(start + i0 + u) * channels + cc] = from_float<T>(fmaf(skip, xs[u], y[u]) * gate[u]);
     }
   }
   if (live) {

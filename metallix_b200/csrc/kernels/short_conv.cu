@@ -55,6 +55,149 @@ short_conv_kernel(const T* __restrict__ x, long long ldx, const float* __restric
   *dst = from_float<T>(acc);
 }
 
+// The same for whole vectors of 16 bytes: a thread owns V neighbouring
+// channels (their weights in registers, up to kConvRegisterTaps taps) and a
+// run of kConvRun consecutive tokens, whose taps overlap. Needs channels and
+// ldx to be multiples of V and 16-byte aligned x, w and out.
+constexpr int kConvRegisterTaps = 4;
+
+template <typename T> struct ConvVector;
+template <> struct ConvVector<float> {
+  static constexpr int V = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct ConvVector<__nv_bfloat16> {
+  static constexpr int V = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(words[i] << 16);
+      v[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t words[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      words[i] = *reinterpret_cast<uint32_t*>(&pair);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(words[0], words[1], words[2], words[3]);
+  }
+};
+
+constexpr int kConvRun = 4;     // consecutive tokens a thread of the vector kernel works through
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(kConvThreads)
+short_conv_vector_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ w,
+                         const float* __restrict__ bias, const float* __restrict__ state,
+                         const int* __restrict__ token_request, const int* __restrict__ row_start,
+                         const int* __restrict__ row_length, const int* __restrict__ request_slots,
+                         T* __restrict__ out, int tokens, int channels, int num_slots, int residual,
+                         int activation, int* status) {
+  constexpr int V = ConvVector<T>::V, MAXT = kConvRegisterTaps, WINDOW = kConvRun + MAXT - 1, taps = TAPS;
+  const int c = (blockIdx.x * kConvThreads + threadIdx.x) * V;
+  if (c >= channels) return;
+  constexpr int before = taps - 1;
+  const int first = blockIdx.y * kConvRun;
+  // Tap j of token t is row t - before + j of x wherever that row is the same
+  // request's. So the rows first - before ... first + kConvRun - 1 are all
+  // the run needs of x; they and the weights are asked for at once, before
+  // the requests are looked up, and only a request's first tokens go to the
+  // state instead. window[m] is row first - (MAXT - 1) + m.
+  float window[WINDOW][V];
+#pragma unroll
+  for (int m = 0; m < WINDOW; ++m) {
+    const int at = first - (MAXT - 1) + m;
+    if (m >= MAXT - 1 - before && at >= 0 && at < tokens) ConvVector<T>::load(x + static_cast<size_t>(at) * ldx + c, window[m]);
+  }
+  float wr[MAXT][V], base[V];
+  if (taps == MAXT) {     // the V channels' weights lie side by side: whole vectors
+    float flat[V * MAXT];
+#pragma unroll
+    for (int i = 0; i < V * MAXT; i += 4) {
+      const float4 q = *reinterpret_cast<const float4*>(w + static_cast<size_t>(c) * MAXT + i);
+      flat[i] = q.x; flat[i + 1] = q.y; flat[i + 2] = q.z; flat[i + 3] = q.w;
+    }
+#pragma unroll
+    for (int j = 0; j < MAXT; ++j)
+#pragma unroll
+      for (int v = 0; v < V; ++v) wr[j][v] = flat[v * MAXT + j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < MAXT; ++j)
+#pragma unroll
+      for (int v = 0; v < V; ++v) wr[j][v] = j < taps ? w[static_cast<size_t>(c + v) * taps + j] : 0.0f;
+  }
+#pragma unroll
+  for (int v = 0; v < V; ++v) base[v] = bias != nullptr ? bias[c + v] : 0.0f;
+  int row = -1, n = 0, slot = 0, start = 0;     // the request row of the token before, and what was looked up for it
+#pragma unroll
+  for (int r = 0; r < kConvRun; ++r) {
+    const int t = first + r;
+    if (t >= tokens) break;
+    const int now = token_request[t];
+    if (now != row) {
+      row = now;
+      n = row_length[row];
+      slot = n > 0 ? request_slots[row] : 0;
+      start = row_start[row];
+    }
+    T* dst = out + static_cast<size_t>(t) * channels + c;
+    float acc[V];
+    if (n <= 0 || slot < 0 || slot >= num_slots) {
+      if (n > 0 && c == 0) atomicOr(status, kStatusBadSlot);
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v] = 0.0f;
+      ConvVector<T>::store(dst, acc);
+      continue;
+    }
+    const int i = t - start;
+    const float* held = state + static_cast<size_t>(slot) * before * channels + c;
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = base[v];
+#pragma unroll
+    for (int j = 0; j < MAXT; ++j) {
+      if (j < taps) {
+        const int rel = i - before + j;
+        float value[V];
+        if (rel < 0) {
+#pragma unroll
+          for (int v = 0; v < V; ++v) value[v] = held[static_cast<size_t>(before + rel) * channels + v];
+        } else {
+          // row t - before + j = first - (MAXT - 1) + m: a constant m once the loops are unrolled
+#pragma unroll
+          for (int m = 0; m < WINDOW; ++m)
+            if (m == r - before + j + MAXT - 1) {
+#pragma unroll
+              for (int v = 0; v < V; ++v) value[v] = window[m][v];
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = fmaf(wr[j][v], value[v], acc[v]);
+        if (residual && j == taps - 1) {
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[v] += value[v];    // the last tap's input is the token's own
+        }
+      }
+    }
+    if (activation == 1) {
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v] = acc[v] / (1.0f + expf(-acc[v]));
+    }
+    ConvVector<T>::store(dst, acc);
+  }
+}
+
 // The state after the row's n tokens: entry k is the input n - (taps - 1) + k
 // of the row if that is one of its tokens, else what entry k + n held. One
 // thread owns a channel's entries and walks them upwards, so an entry is
@@ -84,11 +227,24 @@ static int launch_short_conv(const void* x, long long ldx, const float* w, const
                              const int* token_request, const int* row_start, const int* row_length,
                              const int* request_slots, void* out, int tokens, int rows, int channels, int taps,
                              int num_slots, int residual, int activation, int* status, cudaStream_t stream) {
-  const long long total = static_cast<long long>(tokens) * channels;
-  const unsigned blocks = static_cast<unsigned>((total + kConvThreads - 1) / kConvThreads);
-  short_conv_kernel<T><<<blocks, kConvThreads, 0, stream>>>(
-      static_cast<const T*>(x), ldx, w, bias, state, token_request, row_start, row_length, request_slots,
-      static_cast<T*>(out), tokens, channels, taps, num_slots, residual, activation, status);
+  constexpr int V = ConvVector<T>::V;
+  if (taps <= kConvRegisterTaps && channels % V == 0 && ldx % V == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(w) & 15) == 0 && ceil_div(tokens, kConvRun) <= 65535 &&
+      (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    dim3 grid(ceil_div(channels / V, kConvThreads), ceil_div(tokens, kConvRun));
+#define VECTOR(TAPS)                                                                                               \
+  short_conv_vector_kernel<T, TAPS><<<grid, kConvThreads, 0, stream>>>(                                           \
+      static_cast<const T*>(x), ldx, w, bias, state, token_request, row_start, row_length, request_slots,         \
+      static_cast<T*>(out), tokens, channels, num_slots, residual, activation, status)
+    if (taps == 1) VECTOR(1); else if (taps == 2) VECTOR(2); else if (taps == 3) VECTOR(3); else VECTOR(4);
+#undef VECTOR
+  } else {
+    const long long total = static_cast<long long>(tokens) * channels;
+    const unsigned blocks = static_cast<unsigned>((total + kConvThreads - 1) / kConvThreads);
+    short_conv_kernel<T><<<blocks, kConvThreads, 0, stream>>>(
+        static_cast<const T*>(x), ldx, w, bias, state, token_request, row_start, row_length, request_slots,
+        static_cast<T*>(out), tokens, channels, taps, num_slots, residual, activation, status);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || taps <= 1) return static_cast<int>(e);
   dim3 grid(ceil_div(channels, kConvThreads), rows);

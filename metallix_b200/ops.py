@@ -41,7 +41,11 @@ _SIGNATURES = {
     "mxb_selective_scan": [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                            _P, _P],
     "mxb_route_experts": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "mxb_experts_dense_act": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "mxb_expert_rows": [_P, _P, _P, _I, _I, _I, _P],
+    "mxb_expert_rows_tile": [],
+    "mxb_expert_rows_experts": [],
+    "mxb_expert_gather_rows": [_P, _P, _P, _I, _I, _I, _I, _P],
+    "mxb_expert_combine_rows": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "mxb_experts_add_identity": [_P, _P, _P, _I, _I, _I, _P],
     "mxb_experts_routed": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "mxb_add_cast": [_P, _P, _I, _P, _I, _L, _P],
@@ -83,6 +87,7 @@ _SIGNATURES = {
     "mxb_gemm_stream_supported": [_I, _I, _I, _L, _L, _I],
     "mxb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P, _P],
     "mxb_gemm_tcgen05_supported": [_I, _I, _I, _L, _L],
+    "mxb_gemm_tcgen05_grouped": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _P, _P],
     "mxb_silu_mul": [_P, _P, _I, _L, _I, _P],
     "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P, _P],
     "mxb_argmax_pieces": [_I, _I],
@@ -571,16 +576,55 @@ def route_experts(logits: torch.Tensor, correction: torch.Tensor, experts: int, 
     return chosen, weights, dense, on_identity
 
 
-def experts_dense_act(up: torch.Tensor, dense: torch.Tensor, ff: int) -> torch.Tensor:
-    """relu(up)^2 with column e * ff + f of token t times dense[t, e]."""
-    _check(up, "up", tuple(_CODES), 2)
-    _check(dense, "dense", (torch.float32,), 2)
-    tokens, experts = dense.shape
-    _need(up.shape == (tokens, experts * ff), "up must be [tokens, experts * ff]")
-    out = torch.empty_like(up)
-    _call("mxb_experts_dense_act", up.data_ptr(), dense.data_ptr(), out.data_ptr(), tokens, experts, ff,
-          _CODES[up.dtype], _stream())
+def expert_rows(chosen: torch.Tensor, experts: int):
+    """Sorts the (token, choice) pairs by expert. Returns (position int32
+    ``[tokens, top]``: each pair's row in the sorted array, -1 where the choice
+    is not a real expert; tile_group int32 ``[tiles]``: the expert of each tile
+    of ``expert_rows_tile()`` rows, -1 for tiles left empty; the sorted array's
+    rows, every expert's share rounded up to whole tiles)."""
+    _check(chosen, "chosen", (torch.int32,), 2)
+    tile = expert_rows_tile()
+    pairs = chosen.numel()
+    _need(1 <= experts <= int(_fn("mxb_expert_rows_experts")()), "too many experts to sort by")
+    tiles = (pairs + experts * (tile - 1) + tile - 1) // tile
+    position = torch.empty(chosen.shape, dtype=torch.int32, device=chosen.device)
+    tile_group = torch.empty((tiles,), dtype=torch.int32, device=chosen.device)
+    _call("mxb_expert_rows", chosen.data_ptr(), position.data_ptr(), tile_group.data_ptr(), pairs, experts, tiles,
+          _stream())
+    return position, tile_group, tiles * tile
+
+
+def expert_rows_tile() -> int:
+    return int(_fn("mxb_expert_rows_tile")())
+
+
+def expert_gather_rows(h: torch.Tensor, position: torch.Tensor, rows: int) -> torch.Tensor:
+    """``[rows, hidden]`` with h[t] at position[t, k] for every pair that has
+    a position; the other rows are left as they are found."""
+    _check(h, "h", tuple(_CODES), 2)
+    _check(position, "position", (torch.int32,), 2)
+    _need(position.shape[0] == h.shape[0], "a row of positions per token")
+    out = torch.empty((rows, h.shape[1]), dtype=h.dtype, device=h.device)
+    _call("mxb_expert_gather_rows", h.data_ptr(), position.data_ptr(), out.data_ptr(), position.numel(), h.shape[1],
+          position.shape[1], _CODES[h.dtype], _stream())
     return out
+
+
+def expert_combine_rows(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor, on_identity: torch.Tensor,
+                        h: torch.Tensor) -> torch.Tensor:
+    """y[t] = sum_k weights[t, k] rows[position[t, k]] + on_identity[t] h[t], float32."""
+    _check(rows, "rows", (torch.float32,), 2)
+    _check(position, "position", (torch.int32,), 2)
+    _check(weights, "weights", (torch.float32,), 2)
+    _check(on_identity, "on_identity", (torch.float32,), 1)
+    _check(h, "h", tuple(_CODES), 2)
+    tokens, hidden = h.shape
+    _need(rows.shape[1] == hidden and position.shape == weights.shape and position.shape[0] == tokens
+          and on_identity.numel() == tokens, "rows, positions, weights and h do not fit")
+    y = torch.empty((tokens, hidden), dtype=torch.float32, device=h.device)
+    _call("mxb_expert_combine_rows", rows.data_ptr(), position.data_ptr(), weights.data_ptr(), on_identity.data_ptr(),
+          h.data_ptr(), y.data_ptr(), tokens, hidden, position.shape[1], _CODES[h.dtype], _stream())
+    return y
 
 
 def experts_add_identity(y: torch.Tensor, h: torch.Tensor, on_identity: torch.Tensor) -> torch.Tensor:
@@ -600,7 +644,7 @@ def experts_routed(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ch
     experts e = chosen[t, k] < experts, plus h_t times the weights of chosen
     indices from ``experts`` on; float32 ``[tokens, hidden]``. Only the chosen
     experts' weights are read. w_up ``[experts * ff, hidden]``, w_down
-    ``[hidden, experts * ff]``."""
+    ``[experts * hidden, ff]``."""
     dtype = h.dtype
     _check(h, "h", tuple(_CODES), 2)
     _check(w_up, "w_up", (dtype,), 2)
@@ -610,7 +654,7 @@ def experts_routed(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ch
     tokens, hidden = h.shape
     top = chosen.shape[1]
     _need(chosen.shape == (tokens, top) and weights.shape == (tokens, top), "chosen and weights must be [tokens, top]")
-    _need(w_up.shape == (experts * ff, hidden) and w_down.shape == (hidden, experts * ff),
+    _need(w_up.shape == (experts * ff, hidden) and w_down.shape == (experts * hidden, ff),
           "the experts' stacked weights do not fit")
     act = torch.empty((tokens * top, ff), dtype=torch.float32, device=h.device)
     y = torch.empty((tokens, hidden), dtype=torch.float32, device=h.device)

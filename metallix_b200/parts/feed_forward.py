@@ -96,9 +96,10 @@ class RoutedExperts:
     outputs; the ``top`` largest s + correction are chosen; weights are the
     chosen s over their sum (+ 1e-20); d = sum_k weight_k expert_k(m), an
     expert being Wdown act(Wup m) or, for the last ``identity`` outputs, m
-    itself. Steps of up to ``ROUTED_TOKENS`` tokens read only the chosen
-    experts' weights; larger ones run all experts as two stacked products with
-    the weights (zero for experts not chosen) applied in between."""
+    itself. Steps of up to ``ROUTED_TOKENS`` tokens, and float32, go row by
+    row through the chosen experts' weights; larger steps sort the (token,
+    choice) pairs by expert and run two grouped tensor-core products over
+    them, each tile of rows against its expert's matrices."""
 
     kind = "routed_experts"
     ROUTED_TOKENS = 16
@@ -120,9 +121,9 @@ class RoutedExperts:
                                  f"expected {(ff, hidden)} and {(hidden, ff)}")
             ups.append(up.to(runtime.device))
             downs.append(down.to(runtime.device))
-        # up: rows e * ff + f; down: columns e * ff + f, so that an expert's block of a row is contiguous
+        # up: rows e * ff + f; down: rows e * hidden + c: one expert's matrix after the other
         self.up = Linear(torch.cat(ups, dim=0), runtime) if ups else None
-        self.down = Linear(torch.cat(downs, dim=1), runtime) if downs else None
+        self.down = Linear(torch.cat(downs, dim=0), runtime) if downs else None
         router = weights.take(spec["router"])
         if tuple(router.shape) != (outputs, hidden):
             raise ValueError(f"{spec['router']} is {tuple(router.shape)}, expected {(outputs, hidden)}")
@@ -139,11 +140,21 @@ class RoutedExperts:
         chosen, weights, dense, on_identity = ops.route_experts(logits, self.correction, self.experts, self.top)
         if self.up is None:     # identity experts only
             return ops.experts_add_identity(torch.zeros(x.shape, dtype=torch.float32, device=x.device), x, on_identity)
-        if x.shape[0] <= self.ROUTED_TOKENS:
-            return ops.experts_routed(x, self.up.weight, self.down.weight, chosen, weights, self.experts,
-                                      self.intermediate_size)
-        act = ops.experts_dense_act(self.up.forward(x), dense, self.intermediate_size)
-        return ops.experts_add_identity(self.down.forward(act, out_dtype=torch.float32), x, on_identity)
+        if x.shape[0] > self.ROUTED_TOKENS and self.grouped(x):
+            from .. import tensor_core
+            position, tile_group, rows = ops.expert_rows(chosen, self.experts)
+            act = tensor_core.gemm_grouped(ops.expert_gather_rows(x, position, rows), self.up.weight, tile_group,
+                                           self.experts, tensor_core.RELU_SQUARED)
+            out = tensor_core.gemm_grouped(act, self.down.weight, tile_group, self.experts, tensor_core.STORE_F32)
+            return ops.expert_combine_rows(out, position, weights, on_identity, x)
+        return ops.experts_routed(x, self.up.weight, self.down.weight, chosen, weights, self.experts,
+                                  self.intermediate_size)
+
+    def grouped(self, x: torch.Tensor) -> bool:
+        """Whether the grouped tensor-core products take this step."""
+        from .. import tensor_core
+        return (self.intermediate_size % 8 == 0 and self.down.weight.data_ptr() % 16 == 0
+                and tensor_core.supports(x, self.up.weight, torch.bfloat16))
 
     def weight_bytes(self) -> int:
         """What a decode step of one token reads: the router and ``top`` experts."""

@@ -478,9 +478,11 @@ def test_router_choice_by_corrected_scores_weights_by_scores(outputs, real, top)
 @pytest.mark.parametrize("width, ff, count, identity, top", [(72, 24, 5, 1, 2), (48, 8, 1, 3, 2), (128, 64, 8, 2, 4),
                                                               (40, 20, 2, 0, 2), (96, 33, 7, 0, 1), (64, 16, 0, 3, 2)])
 def test_routed_experts_both_ways_through_them(dtype, width, ff, count, identity, top):
-    """The feed-forward part on a few tokens (only the chosen experts' weights
-    are read) and on many (all experts as two stacked products) against the
-    plain mixture; identity experts return their input."""
+    """The feed-forward part on a few tokens (row by row through the chosen
+    experts' weights) and on many (in 16 bits the pairs sorted by expert and
+    two grouped products, where the sizes allow them; several tiles for an
+    expert at 700 tokens) against the plain mixture; identity experts return
+    their input."""
     from metallix_b200.config.spec import PartSpec
     from metallix_b200.parts.registry import Runtime, StepContext, WeightStore, build_part  # noqa: F401
     torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
@@ -497,7 +499,7 @@ def test_routed_experts_both_ways_through_them(dtype, width, ff, count, identity
         "hidden_size": width, "intermediate_size": ff, "experts": count, "identity": identity, "top": top,
         "activation": "relu_squared", "up_proj": "m.e{}.up", "down_proj": "m.e{}.down", "router": "m.router",
         "correction": "m.correction"}), store, runtime)
-    for tokens in (1, 5, part.ROUTED_TOKENS, part.ROUTED_TOKENS + 1, 70):
+    for tokens in (1, 5, part.ROUTED_TOKENS, part.ROUTED_TOKENS + 1, 70, 300, 700):
         h = rounded(rng.normal(size=(tokens, width)), torch_dtype)
         chosen = []
         want = plain.expert_mixture(h, tensors, "m", experts=count, identity=identity, top=top, chosen_out=chosen)
@@ -510,6 +512,58 @@ def test_routed_experts_both_ways_through_them(dtype, width, ff, count, identity
             assert np.median(errors) < 3e-2 and (errors < 3e-2).mean() >= 0.9
         if identity and count:
             assert (chosen[0] >= count).any() or tokens < 5       # identity experts do get chosen
+
+
+@gpu
+@pytest.mark.parametrize("tokens, top, experts, extra, k, n", [(300, 2, 5, 1, 72, 40), (700, 3, 4, 0, 64, 136),
+                                                                (40, 1, 9, 2, 136, 264), (1000, 2, 3, 1, 200, 64)])
+def test_pairs_sorted_by_expert_and_the_grouped_product(tokens, top, experts, extra, k, n):
+    """Every (token, choice) pair gets a row of its own inside its expert's
+    tiles, choices that are no real expert get none, and the grouped product
+    multiplies each tile by its expert's matrix (against a float32 product row
+    by row), with and without the squared relu; an expert without tokens has
+    no tile."""
+    from metallix_b200 import ops, tensor_core
+    rng = np.random.default_rng(tokens + k)
+    chosen = rng.integers(0, experts + extra, size=(tokens, top)).astype(np.int32)
+    chosen[chosen == 1] = 0                                     # expert 1 stays without tokens
+    position, tile_group, rows = ops.expert_rows(dev(chosen, torch.int32), experts)
+    tile = ops.expert_rows_tile()
+    position, tile_group = position.cpu().numpy(), tile_group.cpu().numpy()
+    assert rows == tile * len(tile_group) and rows >= tokens * top
+    real = chosen < experts
+    assert (position[~real] == -1).all() and (position[real] >= 0).all()
+    assert len(np.unique(position[real])) == real.sum()         # no row is given twice
+    assert np.array_equal(tile_group[position[real] // tile], chosen[real])
+    used = tile_group[tile_group >= 0]
+    assert (np.diff(used) >= 0).all() and 1 not in used and (tile_group[len(used):] == -1).all()
+    for e in range(experts):                                    # an expert's rows fill its tiles from the front
+        mine = np.sort(position[chosen == e])
+        if len(mine):
+            assert np.array_equal(mine, mine[0] + np.arange(len(mine))) and mine[0] % tile == 0
+            assert (tile_group == e).sum() == -(-len(mine) // tile)
+    h = rounded(rng.normal(size=(tokens, k)), torch.bfloat16)
+    w = rounded(rng.normal(size=(experts * n, k)) * 0.2, torch.bfloat16)
+    sorted_rows = ops.expert_gather_rows(dev(h, torch.bfloat16), dev(position, torch.int32), rows)
+    group = dev(tile_group, torch.int32)
+    plain_product = np.einsum("tk,tnk->tn", h[:, None, :].repeat(top, 1).reshape(-1, k),
+                              w.reshape(experts, n, k)[np.minimum(chosen, experts - 1).reshape(-1)])
+    where = position.reshape(-1)
+    for epilogue, want in ((tensor_core.STORE_F32, plain_product),
+                           (tensor_core.RELU_SQUARED, np.maximum(plain_product, 0.0) ** 2)):
+        got = tensor_core.gemm_grouped(sorted_rows, dev(w, torch.bfloat16), group, experts, epilogue)
+        got = got.double().cpu().numpy()[where[where >= 0]]
+        bound = 1e-4 if epilogue == tensor_core.STORE_F32 else 2e-2
+        assert np.abs(got - want[where >= 0]).max() < bound * max(1.0, np.abs(want).max())
+    weights = rng.random(size=(tokens, top)).astype(np.float32)
+    on_identity = rng.random(size=tokens).astype(np.float32)
+    out_rows = rng.normal(size=(rows, k)).astype(np.float32)
+    got = ops.expert_combine_rows(dev(out_rows), dev(position, torch.int32), dev(weights), dev(on_identity),
+                                  dev(h, torch.bfloat16)).double().cpu().numpy()
+    want = on_identity[:, None] * h
+    for j in range(top):
+        want = want + np.where(position[:, j:j + 1] >= 0, weights[:, j:j + 1] * out_rows[np.maximum(position[:, j], 0)], 0.0)
+    assert np.abs(got - want).max() < 1e-5
 
 
 @gpu
