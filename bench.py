@@ -1156,7 +1156,7 @@ def design_sadosun(args):
     for tokens in (8, prompt * 4):
         x, delta, ones = normal(tokens, hidden), normal(tokens, hidden).to(bf16), torch.ones(hidden, device="cuda")
         normed = normal(tokens, hidden).to(bf16)
-        conv_w, conv_state = normal(hidden, taps), torch.zeros(2, taps - 1, hidden, device="cuda")
+        conv_w, conv_state = normal(taps, hidden), torch.zeros(2, taps - 1, hidden, device="cuda")
         owner, start, length, slot = ints([0] * tokens), ints([0]), ints([tokens]), ints([0])
         if tokens == 8:     # eight requests of one token
             owner, start, length, slot = ints(range(8)), ints(range(8)), ints([1] * 8), ints([0, 1] * 4)

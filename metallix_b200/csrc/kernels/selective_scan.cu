@@ -23,7 +23,7 @@ constexpr int kScanThreads = 128;      // 32 channels a block
 
 __device__ __forceinline__ float softplus_of(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
-template <typename T, int PER>
+template <typename T, int PER, int AHEAD>
 __global__ void __launch_bounds__(kScanThreads)
 selective_scan_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ step, long long ld_step,
                       const float* __restrict__ step_bias, const float* __restrict__ a, const T* __restrict__ b,
@@ -58,53 +58,119 @@ selective_scan_kernel(const T* __restrict__ x, long long ldx, const float* __res
   // size, decays, increments, gate) does not wait for the token before. So
   // AHEAD tokens are fetched and prepared side by side, then stepped through.
   // A token past the row's end repeats the last one's loads with a decay of
-  // one and an increment of zero, which leaves the state as it is.
-  constexpr int AHEAD = PER <= 4 ? 8 : (PER <= 16 ? 2 : 1);
-  for (int i0 = 0; i0 < n; i0 += AHEAD) {
-    float pv[AHEAD], xs[AHEAD], zs[AHEAD];
-    T bs[AHEAD][PER], cs[AHEAD][PER];
+  // one and an increment of zero, which leaves the state as it is. A step of
+  // single tokens (a decode step) takes AHEAD = 1.
+  if constexpr (AHEAD >= kScanLanes) {
+    // What belongs to a token and not to a state (its step size, its input
+    // times the step size, its gate) is the same for the lanes that share a
+    // channel: lane l works it out for the tokens l, l + 4, ... of the batch
+    // and hands it round; it also writes those tokens' outputs.
+    constexpr int OWN = AHEAD / kScanLanes;
+    for (int i0 = 0; i0 < n; i0 += AHEAD) {
+      float own_dt[OWN], own_dx[OWN], own_x[OWN], own_gate[OWN];
+      T bs[AHEAD][PER], cs[AHEAD][PER];
 #pragma unroll
-    for (int u = 0; u < AHEAD; ++u) {
-      const size_t t = static_cast<size_t>(start + (i0 + u < n ? i0 + u : n - 1));
-      pv[u] = step[t * ld_step + cc];
-      xs[u] = to_float(x[t * ldx + cc]);
-      zs[u] = to_float(z[t * ldz + cc]);
+      for (int h = 0; h < OWN; ++h) {
+        const int i = i0 + lane + kScanLanes * h;
+        const size_t t = static_cast<size_t>(start + (i < n ? i : n - 1));
+        own_dt[h] = step[t * ld_step + cc];
+        own_x[h] = to_float(x[t * ldx + cc]);
+        own_gate[h] = to_float(z[t * ldz + cc]);
+      }
 #pragma unroll
-      for (int j = 0; j < PER; ++j) {
-        const int k = lane + kScanLanes * j;
-        bs[u][j] = k < states ? b[t * ldbc + k] : from_float<T>(0.0f);   // a state that is not there stays at zero
-        cs[u][j] = k < states ? c[t * ldbc + k] : from_float<T>(0.0f);
+      for (int u = 0; u < AHEAD; ++u) {
+        const size_t t = static_cast<size_t>(start + (i0 + u < n ? i0 + u : n - 1));
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          const int k = lane + kScanLanes * j;
+          bs[u][j] = k < states ? b[t * ldbc + k] : from_float<T>(0.0f);   // a state that is not there stays at zero
+          cs[u][j] = k < states ? c[t * ldbc + k] : from_float<T>(0.0f);
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < OWN; ++h) {
+        own_dt[h] = softplus_of(own_dt[h] + bias);
+        own_dx[h] = own_dt[h] * own_x[h];
+        own_gate[h] = own_gate[h] / (1.0f + expf(-own_gate[h]));
+      }
+      float keep[AHEAD][PER], add[AHEAD][PER], y[AHEAD];
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        const bool valid = i0 + u < n;
+        const float dt = __shfl_sync(0xffffffffu, own_dt[u / kScanLanes], u % kScanLanes, kScanLanes);
+        const float dx = __shfl_sync(0xffffffffu, own_dx[u / kScanLanes], u % kScanLanes, kScanLanes);
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          keep[u][j] = valid ? expf(dt * decay[j]) : 1.0f;
+          add[u][j] = valid ? dx * to_float(bs[u][j]) : 0.0f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          s[j] = fmaf(keep[u][j], s[j], add[u][j]);
+          sum = fmaf(s[j], to_float(cs[u][j]), sum);
+        }
+        y[u] = sum;
+      }
+#pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        y[u] += __shfl_xor_sync(0xffffffffu, y[u], 1);
+        y[u] += __shfl_xor_sync(0xffffffffu, y[u], 2);
+        if (lane == u % kScanLanes && live && i0 + u < n)
+          out[static_cast<size_t>(start + i0 + u) * channels + cc] =
+              from_float<T>(fmaf(skip, own_x[u / kScanLanes], y[u]) * own_gate[u / kScanLanes]);
       }
     }
-    float keep[AHEAD][PER], add[AHEAD][PER], gate[AHEAD], y[AHEAD];
-#pragma unroll
-    for (int u = 0; u < AHEAD; ++u) {
-      const bool valid = i0 + u < n;
-      const float dt = softplus_of(pv[u] + bias);
-      const float dx = dt * xs[u];
-#pragma unroll
-      for (int j = 0; j < PER; ++j) {
-        keep[u][j] = valid ? expf(dt * decay[j]) : 1.0f;
-        add[u][j] = valid ? dx * to_float(bs[u][j]) : 0.0f;
+  } else {
+    for (int i0 = 0; i0 < n; i0 += AHEAD) {
+      float pv[AHEAD], xs[AHEAD], zs[AHEAD];
+      T bs[AHEAD][PER], cs[AHEAD][PER];
+  #pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        const size_t t = static_cast<size_t>(start + (i0 + u < n ? i0 + u : n - 1));
+        pv[u] = step[t * ld_step + cc];
+        xs[u] = to_float(x[t * ldx + cc]);
+        zs[u] = to_float(z[t * ldz + cc]);
+  #pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          const int k = lane + kScanLanes * j;
+          bs[u][j] = k < states ? b[t * ldbc + k] : from_float<T>(0.0f);   // a state that is not there stays at zero
+          cs[u][j] = k < states ? c[t * ldbc + k] : from_float<T>(0.0f);
+        }
       }
-      gate[u] = zs[u] / (1.0f + expf(-zs[u]));
-    }
-#pragma unroll
-    for (int u = 0; u < AHEAD; ++u) {
-      float sum = 0.0f;
-#pragma unroll
-      for (int j = 0; j < PER; ++j) {
-        s[j] = fmaf(keep[u][j], s[j], add[u][j]);
-        sum = fmaf(s[j], to_float(cs[u][j]), sum);
+      float keep[AHEAD][PER], add[AHEAD][PER], gate[AHEAD], y[AHEAD];
+  #pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        const bool valid = i0 + u < n;
+        const float dt = softplus_of(pv[u] + bias);
+        const float dx = dt * xs[u];
+  #pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          keep[u][j] = valid ? expf(dt * decay[j]) : 1.0f;
+          add[u][j] = valid ? dx * to_float(bs[u][j]) : 0.0f;
+        }
+        gate[u] = zs[u] / (1.0f + expf(-zs[u]));
       }
-      y[u] = sum;
-    }
-#pragma unroll
-    for (int u = 0; u < AHEAD; ++u) {
-      y[u] += __shfl_xor_sync(0xffffffffu, y[u], 1);
-      y[u] += __shfl_xor_sync(0xffffffffu, y[u], 2);
-      if (lane == 0 && live && i0 + u < n)
-        out[static_cast<size_t>(start + i0 + u) * channels + cc] = from_float<T>(fmaf(skip, xs[u], y[u]) * gate[u]);
+  #pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        float sum = 0.0f;
+  #pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          s[j] = fmaf(keep[u][j], s[j], add[u][j]);
+          sum = fmaf(s[j], to_float(cs[u][j]), sum);
+        }
+        y[u] = sum;
+      }
+  #pragma unroll
+      for (int u = 0; u < AHEAD; ++u) {
+        y[u] += __shfl_xor_sync(0xffffffffu, y[u], 1);
+        y[u] += __shfl_xor_sync(0xffffffffu, y[u], 2);
+        if (lane == 0 && live && i0 + u < n)
+          out[static_cast<size_t>(start + i0 + u) * channels + cc] = from_float<T>(fmaf(skip, xs[u], y[u]) * gate[u]);
+      }
     }
   }
   if (live) {
@@ -121,12 +187,16 @@ static int launch_scan(const void* x, long long ldx, const float* step, long lon
                        const float* a, const void* b, const void* c, long long ldbc, const float* d, const void* z,
                        long long ldz, float* state, const int* row_start, const int* row_length,
                        const int* request_slots, void* out, int rows, int channels, int states, int num_slots,
-                       int* status, cudaStream_t stream) {
+                       int longest, int* status, cudaStream_t stream) {
   dim3 grid(ceil_div(channels, kScanThreads / kScanLanes), rows);
-  selective_scan_kernel<T, PER><<<grid, kScanThreads, 0, stream>>>(
-      static_cast<const T*>(x), ldx, step, ld_step, step_bias, a, static_cast<const T*>(b), static_cast<const T*>(c),
-      ldbc, d, static_cast<const T*>(z), ldz, state, row_start, row_length, request_slots, static_cast<T*>(out),
-      channels, states, num_slots, status);
+  constexpr int ahead = PER <= 4 ? 8 : (PER <= 16 ? 2 : 1);
+#define SCAN(AHEAD)                                                                                                  \
+  selective_scan_kernel<T, PER, AHEAD><<<grid, kScanThreads, 0, stream>>>(                                          \
+      static_cast<const T*>(x), ldx, step, ld_step, step_bias, a, static_cast<const T*>(b), static_cast<const T*>(c), \
+      ldbc, d, static_cast<const T*>(z), ldz, state, row_start, row_length, request_slots, static_cast<T*>(out),    \
+      channels, states, num_slots, status)
+  if (longest == 1 || ahead == 1) SCAN(1); else SCAN(ahead);
+#undef SCAN
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -136,17 +206,17 @@ using namespace mxb;
 
 // x, z: [tokens, channels] (row strides ldx, ldz); step: float32 [tokens, channels] ahead of its bias and softplus;
 // a: float32 [channels, states] (negative); b, c: [tokens, states] with row stride ldbc; d: [channels];
-// out: [tokens, channels] contiguous. Up to 256 states.
+// out: [tokens, channels] contiguous. Up to 256 states. longest: the most tokens of a row (0 if not known).
 MXB_API int mxb_selective_scan(const void* x, long long ldx, const float* step, long long ld_step,
                                const float* step_bias, const float* a, const void* b, const void* c, long long ldbc,
                                const float* d, const void* z, long long ldz, float* state, const int* row_start,
                                const int* row_length, const int* request_slots, void* out, int rows, int channels,
-                               int states, int num_slots, int dtype, int* status, cudaStream_t stream) {
+                               int states, int num_slots, int longest, int dtype, int* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (channels <= 0 || states <= 0 || states > 64 * kScanLanes) return static_cast<int>(cudaErrorInvalidValue);
   const int per = ceil_div(states, kScanLanes);
 #define ARGS x, ldx, step, ld_step, step_bias, a, b, c, ldbc, d, z, ldz, state, row_start, row_length, request_slots, \
-             out, rows, channels, states, num_slots, status, stream
+             out, rows, channels, states, num_slots, longest, status, stream
 #define DISPATCH(T)                                    \
   if (per <= 1) return launch_scan<T, 1>(ARGS);        \
   if (per <= 2) return launch_scan<T, 2>(ARGS);        \

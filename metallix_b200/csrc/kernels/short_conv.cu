@@ -2,11 +2,12 @@
 // packed tokens of a step, with the inputs it still needs from earlier steps
 // kept per request.
 //
-//   y_t[c] = bias[c] + sum_j w[c, j] * x_(t - taps + 1 + j)[c]        (zeros before the sequence's start)
+//   y_t[c] = bias[c] + sum_j w[j, c] * x_(t - taps + 1 + j)[c]        (zeros before the sequence's start)
 //
 // and then, by choice, out = x + y (the convolution as a correction of its
-// own input) and / or out = silu(out). The last column of w is the current
-// token's. A request row's tokens are consecutive; what lies before the first
+// own input) and / or out = silu(out). w is tap-major, [taps, channels], so
+// that neighbouring channels' weights lie side by side; its last row is the
+// current token's. A request row's tokens are consecutive; what lies before the first
 // of them comes from `state` [slots, taps - 1, channels] (float32; entry k is
 // the input taps - 1 - k tokens before the row's first), which a second
 // kernel then moves on by the row's tokens. A row of length 0 (a padding row
@@ -42,13 +43,12 @@ short_conv_kernel(const T* __restrict__ x, long long ldx, const float* __restric
   }
   const int before = taps - 1;
   const float* held = state + static_cast<size_t>(slot) * before * channels + c;
-  const float* wc = w + static_cast<size_t>(c) * taps;
   float acc = bias != nullptr ? bias[c] : 0.0f;
   for (int j = 0; j < taps; ++j) {
     const int rel = i - before + j;
     const float v = rel >= 0 ? to_float(x[static_cast<size_t>(start + rel) * ldx + c])
                              : held[static_cast<size_t>(before + rel) * channels];
-    acc = fmaf(wc[j], v, acc);
+    acc = fmaf(w[static_cast<size_t>(j) * channels + c], v, acc);
   }
   if (residual) acc += to_float(x[static_cast<size_t>(t) * ldx + c]);
   if (activation == 1) acc = acc / (1.0f + expf(-acc));
@@ -121,22 +121,15 @@ short_conv_vector_kernel(const T* __restrict__ x, long long ldx, const float* __
     if (m >= MAXT - 1 - before && at >= 0 && at < tokens) ConvVector<T>::load(x + static_cast<size_t>(at) * ldx + c, window[m]);
   }
   float wr[MAXT][V], base[V];
-  if (taps == MAXT) {     // the V channels' weights lie side by side: whole vectors
-    float flat[V * MAXT];
 #pragma unroll
-    for (int i = 0; i < V * MAXT; i += 4) {
-      const float4 q = *reinterpret_cast<const float4*>(w + static_cast<size_t>(c) * MAXT + i);
-      flat[i] = q.x; flat[i + 1] = q.y; flat[i + 2] = q.z; flat[i + 3] = q.w;
+  for (int j = 0; j < MAXT; ++j) {
+    if (j < taps) {
+#pragma unroll
+      for (int v = 0; v < V; v += 4) {
+        const float4 q = *reinterpret_cast<const float4*>(w + static_cast<size_t>(j) * channels + c + v);
+        wr[j][v] = q.x; wr[j][v + 1] = q.y; wr[j][v + 2] = q.z; wr[j][v + 3] = q.w;
+      }
     }
-#pragma unroll
-    for (int j = 0; j < MAXT; ++j)
-#pragma unroll
-      for (int v = 0; v < V; ++v) wr[j][v] = flat[v * MAXT + j];
-  } else {
-#pragma unroll
-    for (int j = 0; j < MAXT; ++j)
-#pragma unroll
-      for (int v = 0; v < V; ++v) wr[j][v] = j < taps ? w[static_cast<size_t>(c + v) * taps + j] : 0.0f;
   }
 #pragma unroll
   for (int v = 0; v < V; ++v) base[v] = bias != nullptr ? bias[c + v] : 0.0f;
@@ -257,7 +250,7 @@ static int launch_short_conv(const void* x, long long ldx, const float* w, const
 
 using namespace mxb;
 
-// x: [tokens, channels] with row stride ldx; w: [channels, taps]; bias: [channels] or null;
+// x: [tokens, channels] with row stride ldx; w: [taps, channels]; bias: [channels] or null;
 // state: [num_slots, taps - 1, channels]; out: [tokens, channels] contiguous, must not overlap x.
 MXB_API int mxb_short_conv(const void* x, long long ldx, const float* w, const float* bias, float* state,
                            const int* token_request, const int* row_start, const int* row_length,

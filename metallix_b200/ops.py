@@ -39,7 +39,7 @@ _SIGNATURES = {
                                  _F, _I, _P, _L, _I, _I, _F, _I, _I, _F, _P, _P],
     "mxb_short_conv": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "mxb_selective_scan": [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
-                           _P, _P],
+                           _I, _P, _P],
     "mxb_route_experts": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "mxb_expert_rows": [_P, _P, _P, _I, _I, _I, _P],
     "mxb_expert_rows_tile": [],
@@ -478,16 +478,16 @@ def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     x ``[tokens, channels]`` (rows may be strided): y_t = bias + sum_j
     w[:, j] x_(t - taps + 1 + j), zeros before a sequence's start; the result is
     y, or x + y with ``residual``, passed through ``activation`` ("silu").
-    ``weight`` is float32 ``[channels, taps]``, its last column the current
-    token's. ``state`` (float32 ``[slots, taps - 1, channels]``) holds each
+    ``weight`` is float32 and tap-major, ``[taps, channels]`` (row j is
+    w[:, j]), its last row the current token's. ``state`` (float32 ``[slots, taps - 1, channels]``) holds each
     request's last inputs of earlier steps and is moved on by this step's;
     request row r owns tokens ``row_start[r] .. + row_length[r]`` and the slot
     ``request_slots[r]`` (a row of length 0 touches nothing)."""
     _need(x.is_cuda and x.dtype in _CODES and x.dim() == 2 and x.stride(1) == 1, "x must be [tokens, channels]")
     tokens, channels = x.shape
     _check(weight, "weight", (torch.float32,), 2)
-    taps = weight.shape[1]
-    _need(weight.shape[0] == channels and 1 <= taps <= 64, "weight must be [channels, taps]")
+    taps = weight.shape[0]
+    _need(weight.shape[1] == channels and 1 <= taps <= 64, "weight must be [taps, channels]")
     if bias is not None:
         _check(bias, "bias", (torch.float32,), 1)
         _need(bias.numel() == channels, "bias must have one value per channel")
@@ -514,13 +514,14 @@ SCAN_STATES = 256   # the most states per channel the scan keeps in registers
 
 def selective_scan(x: torch.Tensor, step: torch.Tensor, step_bias: torch.Tensor, a: torch.Tensor, b: torch.Tensor,
                    c: torch.Tensor, d: torch.Tensor, z: torch.Tensor, state: torch.Tensor, row_start: torch.Tensor,
-                   row_length: torch.Tensor, request_slots: torch.Tensor) -> torch.Tensor:
+                   row_length: torch.Tensor, request_slots: torch.Tensor, longest: int = 0) -> torch.Tensor:
     """S <- exp(dt A) S + dt x B, y = S C + D x, out = y silu(z) per channel,
     token by token along each request row, dt = softplus(step + step_bias).
     x, z ``[tokens, channels]`` and b, c ``[tokens, states]`` in the compute
     type (rows may be strided; b and c share a row stride); ``step`` float32
     ``[tokens, channels]``; ``a`` float32 ``[channels, states]``; ``state``
-    float32 ``[slots, channels, states]``, read and moved on."""
+    float32 ``[slots, channels, states]``, read and moved on. ``longest``: the
+    most tokens of a row if known (1 picks the kernel for single tokens)."""
     dtype = x.dtype
     for name, tensor in (("x", x), ("z", z), ("b", b), ("c", c)):
         _need(tensor.is_cuda and tensor.dtype == dtype and dtype in _CODES and tensor.dim() == 2
@@ -546,7 +547,8 @@ def selective_scan(x: torch.Tensor, step: torch.Tensor, step_bias: torch.Tensor,
     _call("mxb_selective_scan", x.data_ptr(), x.stride(0), step.data_ptr(), step.stride(0), step_bias.data_ptr(),
           a.data_ptr(), b.data_ptr(), c.data_ptr(), b.stride(0), d.data_ptr(), z.data_ptr(), z.stride(0),
           state.data_ptr(), row_start.data_ptr(), row_length.data_ptr(), request_slots.data_ptr(), out.data_ptr(),
-          rows, channels, states, state.shape[0], _CODES[dtype], status_word(x.device).data_ptr(), _stream())
+          rows, channels, states, state.shape[0], int(longest), _CODES[dtype], status_word(x.device).data_ptr(),
+          _stream())
     return out
 
 

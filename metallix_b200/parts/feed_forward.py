@@ -102,7 +102,7 @@ class RoutedExperts:
     them, each tile of rows against its expert's matrices."""
 
     kind = "routed_experts"
-    ROUTED_TOKENS = 16
+    ROUTED_TOKENS = 1     # from two tokens on experts are shared often enough for the grouped products to read less
     ACTIVATIONS = ("relu_squared",)
 
     def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):

@@ -201,7 +201,7 @@ class SelectiveScan:
         mixed = ops.selective_scan(
             u, step, self.step_bias, self.decay, picked[:, self.rank:self.rank + self.states],
             picked[:, self.rank + self.states:], self.skip, both[:, self.inner:], cache.members[0].state,
-            rows["row_start"], rows["row_length"], ctx.request_slots)
+            rows["row_start"], rows["row_length"], ctx.request_slots, longest=rows.get("longest", 0))
         return self.o.forward(mixed)
 
     def weight_bytes(self) -> int:

@@ -36,7 +36,8 @@ class ShortConv:
         weight = weights.take(spec["weight"])
         if tuple(weight.shape) != (self.channels, self.taps):
             raise ValueError(f"{spec['weight']} is {tuple(weight.shape)}, expected {(self.channels, self.taps)}")
-        self.weight = weight.to(device=runtime.device, dtype=torch.float32).contiguous()
+        # tap-major for the kernel: neighbouring channels' weights side by side
+        self.weight = weight.to(device=runtime.device, dtype=torch.float32).t().contiguous()
         self.bias: Optional[torch.Tensor] = None
         if spec.get("bias"):
             bias = weights.take(spec["bias"])

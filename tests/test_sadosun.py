@@ -343,8 +343,9 @@ def rows_of(lengths):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("channels, taps, bias, residual, activation", [
     (72, 3, False, True, None), (40, 2, True, False, "silu"), (100, 5, True, False, "silu"), (331, 4, False, True, None),
-    (7, 9, True, True, "silu")])
-def test_short_convolution_with_its_inputs_in_state_slots(dtype, channels, taps, bias, residual, activation):
+    (7, 9, True, True, "silu"), (264, 4, True, True, None), (64, 1, False, True, "silu")])
+@pytest.mark.parametrize("left", [3, 8])     # columns ahead of x in the wider product: 8 lets whole vectors be read
+def test_short_convolution_with_its_inputs_in_state_slots(dtype, channels, taps, bias, residual, activation, left):
     """Four request rows of unequal length in one launch (a single token, a
     padding row, a row shorter than the taps), continued twice from the slots'
     state, against the plain convolution of each whole sequence; x is a column
@@ -364,8 +365,8 @@ def test_short_convolution_with_its_inputs_in_state_slots(dtype, channels, taps,
     for lengths in pieces:
         starts, owner = rows_of(lengths)
         packed = np.concatenate([x[row][done[row]:done[row] + n] for row, n in enumerate(lengths)])
-        wide = dev(np.pad(packed, ((0, 0), (3, 5))), dtype)
-        out = ops.short_conv(wide[:, 3:3 + channels], dev(w), dev(b) if bias else None, state, dev(owner, torch.int32),
+        wide = dev(np.pad(packed, ((0, 0), (left, 16 - left))), dtype)
+        out = ops.short_conv(wide[:, left:left + channels], dev(np.ascontiguousarray(w.T)), dev(b) if bias else None, state, dev(owner, torch.int32),
                              dev(starts, torch.int32), dev(lengths, torch.int32), dev(slots, torch.int32),
                              residual=residual, activation=activation)
         ops.check_status("cuda")
