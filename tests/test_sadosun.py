@@ -373,7 +373,7 @@ def test_short_convolution_with_its_inputs_in_state_slots(dtype, channels, taps,
         for row, n in enumerate(lengths):
             got[row].append(out[starts[row]:starts[row] + n].double().cpu().numpy())
             done[row] += n
-    assert float(state[4].min()) == 7.0 and float(state[1].abs().max()) == 0.0
+    assert taps == 1 or (float(state[4].min()) == 7.0 and float(state[1].abs().max()) == 0.0)
     for row, total in enumerate(totals):
         if not total:
             continue
@@ -383,7 +383,8 @@ def test_short_convolution_with_its_inputs_in_state_slots(dtype, channels, taps,
         if activation == "silu":
             want = plain.silu(want)
         assert np.abs(np.concatenate(got[row]) - want).max() < (1e-5 if dtype == torch.float32 else 5e-2)
-        assert np.abs(state[slots[row]].double().cpu().numpy() - kept).max() < 1e-6     # the last taps - 1 inputs, as they came
+        if taps > 1:
+            assert np.abs(state[slots[row]].double().cpu().numpy() - kept).max() < 1e-6     # the last taps - 1 inputs, as they came
 
 
 @gpu
