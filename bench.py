@@ -1163,7 +1163,7 @@ def design_sadosun(args):
         kernels[f"sublayer_input_{tokens}"] = {
             "sadosun: h + conv(h) over %d taps, the state moved on" % taps: gbs(
                 tokens * hidden * 2 * 2, lambda: ops.short_conv(normed, conv_w, None, conv_state, owner, start, length,
-                                                                slot, residual=True)),
+                                                                slot, residual=True, longest=1 if tokens == 8 else tokens)),
             "qwen3 (and sadosun): x += d; y = norm(x)": gbs(tokens * hidden * (4 + 4 + 2 + 2),
                                                             lambda: ops.add_rmsnorm(x, delta, ones, 1e-6, bf16))}
         gate, table = normal(tokens, side).to(bf16), normal(DESIGN_VOCAB, DESIGN_LAYERS * side).to(bf16)

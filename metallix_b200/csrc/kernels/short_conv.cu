@@ -10,7 +10,8 @@
 // current token's. A request row's tokens are consecutive; what lies before the first
 // of them comes from `state` [slots, taps - 1, channels] (float32; entry k is
 // the input taps - 1 - k tokens before the row's first), which a second
-// kernel then moves on by the row's tokens. A row of length 0 (a padding row
+// kernel then moves on by the row's tokens; in a step of single tokens the
+// thread that has just read a channel's entries moves them on itself (`fold`). A row of length 0 (a padding row
 // of a captured step) reads and writes no state.
 #include "common.cuh"
 
@@ -21,10 +22,10 @@ constexpr int kConvThreads = 256;
 template <typename T>
 __global__ void __launch_bounds__(kConvThreads)
 short_conv_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ w, const float* __restrict__ bias,
-                  const float* __restrict__ state, const int* __restrict__ token_request,
+                  const float* state, const int* __restrict__ token_request,
                   const int* __restrict__ row_start, const int* __restrict__ row_length,
                   const int* __restrict__ request_slots, T* __restrict__ out, int tokens, int channels, int taps,
-                  int num_slots, int residual, int activation, int* status) {
+                  int num_slots, int residual, int activation, int fold, float* state_out, int* status) {
   const long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (index >= static_cast<long long>(tokens) * channels) return;
   const int t = static_cast<int>(index / channels), c = static_cast<int>(index - static_cast<long long>(t) * channels);
@@ -53,6 +54,12 @@ short_conv_kernel(const T* __restrict__ x, long long ldx, const float* __restric
   if (residual) acc += to_float(x[static_cast<size_t>(t) * ldx + c]);
   if (activation == 1) acc = acc / (1.0f + expf(-acc));
   *dst = from_float<T>(acc);
+  if (fold && n == 1) {     // the row's only token: this thread alone has read these entries
+    float* moved = state_out + static_cast<size_t>(slot) * before * channels + c;
+    for (int k = 0; k < before; ++k)
+      moved[static_cast<size_t>(k) * channels] = k + 1 < before ? moved[static_cast<size_t>(k + 1) * channels]
+                                                                : to_float(x[static_cast<size_t>(t) * ldx + c]);
+  }
 }
 
 // The same for whole vectors of 16 bytes: a thread owns V neighbouring
@@ -64,8 +71,8 @@ constexpr int kConvRegisterTaps = 4;
 template <typename T> struct ConvVector;
 template <> struct ConvVector<float> {
   static constexpr int V = 4;
-  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
-    const float4 q = *reinterpret_cast<const float4*>(p);
+  using Packed = float4;
+  static __device__ __forceinline__ void unpack(const float4& q, float (&v)[4]) {
     v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
   }
   static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
@@ -74,8 +81,8 @@ template <> struct ConvVector<float> {
 };
 template <> struct ConvVector<__nv_bfloat16> {
   static constexpr int V = 8;
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
-    const uint4 q = *reinterpret_cast<const uint4*>(p);
+  using Packed = uint4;
+  static __device__ __forceinline__ void unpack(const uint4& q, float (&v)[8]) {
     const uint32_t words[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -97,13 +104,13 @@ template <> struct ConvVector<__nv_bfloat16> {
 constexpr int kConvRun = 4;     // consecutive tokens a thread of the vector kernel works through
 
 template <typename T, int TAPS>
-__global__ void __launch_bounds__(kConvThreads)
+__global__ void __launch_bounds__(kConvThreads, 3)
 short_conv_vector_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ w,
-                         const float* __restrict__ bias, const float* __restrict__ state,
+                         const float* __restrict__ bias, const float* state,
                          const int* __restrict__ token_request, const int* __restrict__ row_start,
                          const int* __restrict__ row_length, const int* __restrict__ request_slots,
                          T* __restrict__ out, int tokens, int channels, int num_slots, int residual,
-                         int activation, int* status) {
+                         int activation, int fold, float* state_out, int* status) {
   constexpr int V = ConvVector<T>::V, MAXT = kConvRegisterTaps, WINDOW = kConvRun + MAXT - 1, taps = TAPS;
   const int c = (blockIdx.x * kConvThreads + threadIdx.x) * V;
   if (c >= channels) return;
@@ -114,11 +121,12 @@ short_conv_vector_kernel(const T* __restrict__ x, long long ldx, const float* __
   // the run needs of x; they and the weights are asked for at once, before
   // the requests are looked up, and only a request's first tokens go to the
   // state instead. window[m] is row first - (MAXT - 1) + m.
-  float window[WINDOW][V];
+  typename ConvVector<T>::Packed window[WINDOW];     // as loaded: 16 bytes a row
 #pragma unroll
   for (int m = 0; m < WINDOW; ++m) {
     const int at = first - (MAXT - 1) + m;
-    if (m >= MAXT - 1 - before && at >= 0 && at < tokens) ConvVector<T>::load(x + static_cast<size_t>(at) * ldx + c, window[m]);
+    if (m >= MAXT - 1 - before && at >= 0 && at < tokens)
+      window[m] = *reinterpret_cast<const typename ConvVector<T>::Packed*>(x + static_cast<size_t>(at) * ldx + c);
   }
   float wr[MAXT][V], base[V];
 #pragma unroll
@@ -170,10 +178,12 @@ short_conv_vector_kernel(const T* __restrict__ x, long long ldx, const float* __
           // row t - before + j = first - (MAXT - 1) + m: a constant m once the loops are unrolled
 #pragma unroll
           for (int m = 0; m < WINDOW; ++m)
-            if (m == r - before + j + MAXT - 1) {
+            if (m == r - before + j + MAXT - 1) ConvVector<T>::unpack(window[m], value);
+        }
+        if (fold && n == 1 && j >= 1) {    // the row's only token: entry j - 1 has been read, entry j is what it becomes
+          float* moved = state_out + static_cast<size_t>(slot) * before * channels + c + static_cast<size_t>(j - 1) * channels;
 #pragma unroll
-              for (int v = 0; v < V; ++v) value[v] = window[m][v];
-            }
+          for (int v = 0; v < V; v += 4) *reinterpret_cast<float4*>(moved + v) = make_float4(value[v], value[v + 1], value[v + 2], value[v + 3]);
         }
 #pragma unroll
         for (int v = 0; v < V; ++v) acc[v] = fmaf(wr[j][v], value[v], acc[v]);
@@ -219,8 +229,10 @@ template <typename T>
 static int launch_short_conv(const void* x, long long ldx, const float* w, const float* bias, float* state,
                              const int* token_request, const int* row_start, const int* row_length,
                              const int* request_slots, void* out, int tokens, int rows, int channels, int taps,
-                             int num_slots, int residual, int activation, int* status, cudaStream_t stream) {
+                             int num_slots, int residual, int activation, int longest, int* status,
+                             cudaStream_t stream) {
   constexpr int V = ConvVector<T>::V;
+  const int fold = longest == 1 && taps > 1;     // single tokens: the state is moved on by the same launch
   if (taps <= kConvRegisterTaps && channels % V == 0 && ldx % V == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(w) & 15) == 0 && ceil_div(tokens, kConvRun) <= 65535 &&
       (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
@@ -228,7 +240,7 @@ static int launch_short_conv(const void* x, long long ldx, const float* w, const
 #define VECTOR(TAPS)                                                                                               \
   short_conv_vector_kernel<T, TAPS><<<grid, kConvThreads, 0, stream>>>(                                           \
       static_cast<const T*>(x), ldx, w, bias, state, token_request, row_start, row_length, request_slots,         \
-      static_cast<T*>(out), tokens, channels, num_slots, residual, activation, status)
+      static_cast<T*>(out), tokens, channels, num_slots, residual, activation, fold, state, status)
     if (taps == 1) VECTOR(1); else if (taps == 2) VECTOR(2); else if (taps == 3) VECTOR(3); else VECTOR(4);
 #undef VECTOR
   } else {
@@ -236,10 +248,10 @@ static int launch_short_conv(const void* x, long long ldx, const float* w, const
     const unsigned blocks = static_cast<unsigned>((total + kConvThreads - 1) / kConvThreads);
     short_conv_kernel<T><<<blocks, kConvThreads, 0, stream>>>(
         static_cast<const T*>(x), ldx, w, bias, state, token_request, row_start, row_length, request_slots,
-        static_cast<T*>(out), tokens, channels, taps, num_slots, residual, activation, status);
+        static_cast<T*>(out), tokens, channels, taps, num_slots, residual, activation, fold, state, status);
   }
   cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess || taps <= 1) return static_cast<int>(e);
+  if (e != cudaSuccess || taps <= 1 || fold) return static_cast<int>(e);
   dim3 grid(ceil_div(channels, kConvThreads), rows);
   short_conv_state_kernel<T><<<grid, kConvThreads, 0, stream>>>(static_cast<const T*>(x), ldx, state, row_start,
                                                                row_length, request_slots, channels, taps, num_slots);
@@ -252,14 +264,16 @@ using namespace mxb;
 
 // x: [tokens, channels] with row stride ldx; w: [taps, channels]; bias: [channels] or null;
 // state: [num_slots, taps - 1, channels]; out: [tokens, channels] contiguous, must not overlap x.
+// longest: the most tokens of a row (0 if not known; 1: a step of single tokens).
 MXB_API int mxb_short_conv(const void* x, long long ldx, const float* w, const float* bias, float* state,
                            const int* token_request, const int* row_start, const int* row_length,
                            const int* request_slots, void* out, int tokens, int rows, int channels, int taps,
-                           int num_slots, int residual, int activation, int dtype, int* status, cudaStream_t stream) {
+                           int num_slots, int residual, int activation, int longest, int dtype, int* status,
+                           cudaStream_t stream) {
   if (tokens <= 0 || rows <= 0) return 0;
   if (channels <= 0 || taps < 1 || taps > 64) return static_cast<int>(cudaErrorInvalidValue);
 #define ARGS x, ldx, w, bias, state, token_request, row_start, row_length, request_slots, out, tokens, rows, channels, \
-             taps, num_slots, residual, activation, status, stream
+             taps, num_slots, residual, activation, longest, status, stream
   if (dtype == kF32) return launch_short_conv<float>(ARGS);
   if (dtype == kBF16) return launch_short_conv<__nv_bfloat16>(ARGS);
 #undef ARGS

@@ -37,7 +37,7 @@ _SIGNATURES = {
                                _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
                                  _F, _I, _P, _L, _I, _I, _F, _I, _I, _F, _P, _P],
-    "mxb_short_conv": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "mxb_short_conv": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "mxb_selective_scan": [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                            _I, _P, _P],
     "mxb_route_experts": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -473,7 +473,8 @@ def relu_squared(x: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------ short convolution over time
 def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
                token_request: torch.Tensor, row_start: torch.Tensor, row_length: torch.Tensor,
-               request_slots: torch.Tensor, residual: bool = False, activation: Optional[str] = None) -> torch.Tensor:
+               request_slots: torch.Tensor, residual: bool = False, activation: Optional[str] = None,
+               longest: int = 0) -> torch.Tensor:
     """A causal convolution over time on each channel of the packed tokens
     x ``[tokens, channels]`` (rows may be strided): y_t = bias + sum_j
     w[:, j] x_(t - taps + 1 + j), zeros before a sequence's start; the result is
@@ -482,7 +483,9 @@ def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     w[:, j]), its last row the current token's. ``state`` (float32 ``[slots, taps - 1, channels]``) holds each
     request's last inputs of earlier steps and is moved on by this step's;
     request row r owns tokens ``row_start[r] .. + row_length[r]`` and the slot
-    ``request_slots[r]`` (a row of length 0 touches nothing)."""
+    ``request_slots[r]`` (a row of length 0 touches nothing). ``longest``: the
+    most tokens of a row if known; a step of single tokens (1) moves the state
+    on in the same launch."""
     _need(x.is_cuda and x.dtype in _CODES and x.dim() == 2 and x.stride(1) == 1, "x must be [tokens, channels]")
     tokens, channels = x.shape
     _check(weight, "weight", (torch.float32,), 2)
@@ -504,7 +507,7 @@ def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     _call("mxb_short_conv", x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), state.data_ptr(),
           token_request.data_ptr(), row_start.data_ptr(), row_length.data_ptr(), request_slots.data_ptr(),
           out.data_ptr(), tokens, rows, channels, taps, state.shape[0], 1 if residual else 0,
-          1 if activation == "silu" else 0, _CODES[x.dtype], status_word(x.device).data_ptr(), _stream())
+          1 if activation == "silu" else 0, int(longest), _CODES[x.dtype], status_word(x.device).data_ptr(), _stream())
     return out
 
 

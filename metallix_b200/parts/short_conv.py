@@ -59,7 +59,7 @@ class ShortConv:
         rows = request_rows_of(ctx)
         return ops.short_conv(x, self.weight, self.bias, cache.state, ctx.token_request, rows["row_start"],
                               rows["row_length"], ctx.request_slots, residual=self.residual,
-                              activation=self.activation)
+                              activation=self.activation, longest=rows.get("longest", 0))
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * 4

@@ -352,7 +352,8 @@ def test_short_convolution_with_its_inputs_in_state_slots(dtype, channels, taps,
     range of a wider product; an untouched slot keeps its values."""
     from metallix_b200 import ops
     rng = np.random.default_rng(channels * taps)
-    pieces = [[6, 1, 0, 2], [1, 1, 0, 13], [2, 9, 0, 1]]
+    # the last steps bring single tokens only: the launch that reads a slot moves it on as well
+    pieces = [[6, 1, 0, 2], [1, 1, 0, 13], [2, 9, 0, 1], [1, 1, 0, 1], [1, 0, 0, 1], [1, 3, 0, 0]]
     slots = [3, 0, 1, 2]
     w, b = rounded(rng.normal(size=(channels, taps)), torch.float32), rounded(rng.normal(size=channels), torch.float32)
     totals = [sum(p[row] for p in pieces) for row in range(4)]
@@ -368,7 +369,7 @@ def test_short_convolution_with_its_inputs_in_state_slots(dtype, channels, taps,
         wide = dev(np.pad(packed, ((0, 0), (left, 16 - left))), dtype)
         out = ops.short_conv(wide[:, left:left + channels], dev(np.ascontiguousarray(w.T)), dev(b) if bias else None, state, dev(owner, torch.int32),
                              dev(starts, torch.int32), dev(lengths, torch.int32), dev(slots, torch.int32),
-                             residual=residual, activation=activation)
+                             residual=residual, activation=activation, longest=max(lengths))
         ops.check_status("cuda")
         for row, n in enumerate(lengths):
             got[row].append(out[starts[row]:starts[row] + n].double().cpu().numpy())
