@@ -1074,8 +1074,8 @@ def design_zitezen(args):
 # taps of the convolutions ahead of the sublayers and the width of a layer's input from the token. Eight
 # layers: a state-space layer and an attention layer in turn. The window is as long as the contexts by
 # default (--chunk), so that both models' attention does the same work.
-SADOSUN_SIZES = {"0.6b-layers": ((2048, 16, 64, 4), (16, 2, 4, 1152), 4, 64),
-                 "8b-layers": ((8192, 16, 256, 4), (16, 2, 4, 4608), 4, 256)}
+SADOSUN_SIZES = {"0.6b-layers": ((2048, 16, 64, 4), (12, 1, 3, 1536), 4, 64),
+                 "8b-layers": ((8192, 16, 256, 4), (12, 1, 3, 6144), 4, 256)}
 
 
 def _sadosun(hidden, heads, kv_heads, dim, inter, size, window):
