@@ -15,6 +15,7 @@ import os
 from dataclasses import dataclass
 from typing import Any, Dict, Mapping, Optional, Type
 
+from .dimorax import DimoraxConfig
 from .mekazen import MekazenConfig
 from .qwen3 import ConfigError, Qwen3Config
 from .sadosun import SadosunConfig
@@ -136,3 +137,6 @@ register(ZITEZEN)
 SADOSUN = ModelFamily(architecture=SadosunConfig.ARCHITECTURE, model_type=SadosunConfig.MODEL_TYPE,
                       kind="sadosun", config_class=SadosunConfig)
 register(SADOSUN)
+DIMORAX = ModelFamily(architecture=DimoraxConfig.ARCHITECTURE, model_type=DimoraxConfig.MODEL_TYPE,
+                      kind="dimorax", config_class=DimoraxConfig)
+register(DIMORAX)

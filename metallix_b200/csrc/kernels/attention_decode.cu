@@ -931,7 +931,7 @@ __global__ void __launch_bounds__(256)
 paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                              const int* __restrict__ row_token, const int* __restrict__ positions,
                              int rows, int heads, int head_dim, int max_splits, int window, int chunk, int slots,
-                             const T* __restrict__ gate, long long gate_stride, int has_sink, float sink_score,
+                             const T* __restrict__ gate, long long gate_stride, int has_sink, float sink_score, const float* sink_heads,
                              int* status) {
   chain_release();
   const int row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
@@ -979,7 +979,8 @@ paged_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ 
     }
     m = round_max;
   }
-  if (has_sink) l += expf(sink_score - m);   // one more key, without a value, in the denominator
+  // one more key, without a value, in the denominator: one score for all heads, or one per head
+  if (has_sink) l += expf((sink_heads != nullptr ? sink_heads[head] : sink_score) - m);
   float value = acc / l;
   if (gate != nullptr) {
     // an output gate over the concatenated heads: value * sigmoid(g), written
@@ -1012,6 +1013,7 @@ struct DecodeProject {
   // A key without a value that every query sees, with this score (has_sink 0: none).
   int has_sink = 0;
   float sink_score = 0.0f;
+  const float* sink_heads = nullptr;   // one score per query head instead (float32)
 };
 
 template <typename T, int HD, int G>
@@ -1041,7 +1043,7 @@ static int launch_decode(const void* q, const void* cache, void* out, float* par
                                          stream, static_cast<const float*>(partial), static_cast<T*>(out),
                                          row_token, positions, rows, heads, HD, max_splits, window, chunk, 0,
                                          static_cast<const T*>(project.gate), project.gate_stride, project.has_sink,
-                                         project.sink_score, status));
+                                         project.sink_score, project.sink_heads, status));
 }
 
 static int decode_resident_blocks = 444;   // blocks of the decode attention that fit the GPU at once (3 an SM); 0: always one block per tile
@@ -1060,14 +1062,14 @@ static int launch_decode_mma(const void* q, const void* cache, void* out, float*
                                                        positions, rows, project.tokens, heads, project.hidden,
                                                        max_splits, window, chunk, slots, kSplitKeys, kDecodeMinusHuge,
                                                        static_cast<const __nv_bfloat16*>(project.gate),
-                                                       project.gate_stride, project.has_sink, project.sink_score,
+                                                       project.gate_stride, project.has_sink, project.sink_score, project.sink_heads,
                                                        status, stream));
     return static_cast<int>(launch_chained(paged_attention_merge_kernel<__nv_bfloat16>, dim3(rows, heads),
                                            dim3(HD <= 64 ? 64 : (HD <= 128 ? 128 : 256)), 0, stream,
                                            static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out),
                                            row_token, positions, rows, heads, HD, max_splits, window, chunk, slots,
                                            static_cast<const __nv_bfloat16*>(project.gate), project.gate_stride,
-                                           project.has_sink, project.sink_score, status));
+                                           project.has_sink, project.sink_score, project.sink_heads, status));
   };
   static_assert(4 * 8 * (HD + 2) * sizeof(float) <= kSplitKeys * HD * 2, "the merge area must fit over the keys");
   dim3 grid(max_splits, kv_heads, rows);
@@ -1158,7 +1160,7 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
                                        int heads, int kv_heads, int head_dim, int page_tokens,
                                        int num_pages, int max_splits, int window, int chunk, float scale,
                                        int dtype, const void* gate, long long gate_stride, float softcap, int has_sink,
-                                       float sink_score, int* status, cudaStream_t stream) {
+                                       float sink_score, const float* sink_heads, int* status, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (!mxb_paged_attention_decode_supported(head_dim, heads, kv_heads, dtype) || max_splits <= 0)
     return static_cast<int>(cudaErrorInvalidValue);
@@ -1169,6 +1171,7 @@ MXB_API int mxb_paged_attention_decode(const void* q, const void* cache, void* o
   project.softcap = softcap;
   project.has_sink = has_sink;
   project.sink_score = sink_score;
+  project.sink_heads = sink_heads;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
              heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream, project
 #define BY_GROUP(T, HD)                                        \
@@ -1207,7 +1210,7 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
                                                int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
                                                int max_splits, int window, int chunk, float scale, const void* w, long long ldw,
                                                int hidden, float* summands, const void* gate, long long gate_stride,
-                                               float softcap, int has_sink, float sink_score, int* status,
+                                               float softcap, int has_sink, float sink_score, const float* sink_heads, int* status,
                                                cudaStream_t stream) {
   if (rows <= 0 || hidden <= 0 || max_splits <= 0) return static_cast<int>(cudaErrorInvalidValue);
   if (!mxb_paged_attention_decode_project_supported(head_dim, heads, kv_heads, kBF16, tokens, w, ldw))
@@ -1223,6 +1226,7 @@ MXB_API int mxb_paged_attention_decode_project(const void* q, const void* cache,
   project.softcap = softcap;
   project.has_sink = has_sink;
   project.sink_score = sink_score;
+  project.sink_heads = sink_heads;
   void* out = nullptr;
 #define ARGS q, cache, out, partial, block_tables, max_pages, row_token, row_request, positions, rows, \
              heads, kv_heads, page_tokens, num_pages, max_splits, window, chunk, scale, status, stream, project
@@ -1294,7 +1298,7 @@ MXB_API int mxb_paged_attention_decode_noalloc(const void* q, const void* cache,
   if (e != cudaSuccess) return static_cast<int>(e);
   return mxb_paged_attention_decode(q, cache, out, scratch, block_tables, max_pages, row_token,
                                     row_request, positions, rows, heads, kv_heads, head_dim, page_tokens,
-                                    num_pages, splits, window, 0, scale, dtype, nullptr, 0, 0.0f, 0, 0.0f, status, stream);
+                                    num_pages, splits, window, 0, scale, dtype, nullptr, 0, 0.0f, 0, 0.0f, nullptr, status, stream);
 }
 
 MXB_TIMELINE_EXPORT(mxb_timeline_attention)

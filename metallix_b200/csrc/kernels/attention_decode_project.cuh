@@ -32,7 +32,7 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
                             const int* __restrict__ positions, int rows, int tokens, int heads, int hidden,
                             int max_splits, int window, int chunk, int slots, int split_keys, float minus_huge,
                             const __nv_bfloat16* __restrict__ gate, long long gate_stride, int has_sink,
-                            float sink_score, int* status) {
+                            float sink_score, const float* sink_heads, int* status) {
   constexpr int PITCH = HD * 2 + 16;  // bytes per row of a tile: rows a warp reads together fall on all banks
   constexpr int X_ROWS = MB * 8;
   extern __shared__ __align__(128) unsigned char project_shared[];
@@ -165,7 +165,8 @@ decode_merge_project_kernel(const float* __restrict__ partial, const __nv_bfloat
       }
       m = round_max;
     }
-    if (has_sink) l += expf(sink_score - m);   // one more key, without a value, in the denominator
+    // one more key, without a value, in the denominator: one score for all heads, or one per head
+    if (has_sink) l += expf((sink_heads != nullptr ? sink_heads[head] : sink_score) - m);
 #pragma unroll
     for (int h = 0; h < HD / 64; ++h) {
       float2 value = make_float2(acc[h].x / l, acc[h].y / l);
@@ -235,7 +236,7 @@ static cudaError_t launch_merge_project(const float* partial, const __nv_bfloat1
                                         const int* row_token, const int* positions, int rows, int tokens, int heads,
                                         int hidden, int max_splits, int window, int chunk, int slots, int split_keys,
                                         float minus_huge, const __nv_bfloat16* gate, long long gate_stride, int has_sink,
-                                        float sink_score, int* status, cudaStream_t stream) {
+                                        float sink_score, const float* sink_heads, int* status, cudaStream_t stream) {
   const dim3 grid((hidden + kProjectColumns - 1) / kProjectColumns, heads);
 #define GO(MB)                                                                                                       \
   {                                                                                                                  \
@@ -247,7 +248,7 @@ static cudaError_t launch_merge_project(const float* partial, const __nv_bfloat1
     }                                                                                                                \
     return launch_chained(kernel, grid, dim3(kProjectThreads), shared, stream, partial, w, ldw, summands, row_token,  \
                           positions, rows, tokens, heads, hidden, max_splits, window, chunk, slots, split_keys, minus_huge,  \
-                          gate, gate_stride, has_sink, sink_score, status);                                                             \
+                          gate, gate_stride, has_sink, sink_score, sink_heads, status);                                                             \
   }
   if (tokens <= 8) GO(1)
   if (tokens <= 16) GO(2)

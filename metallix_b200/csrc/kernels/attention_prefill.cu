@@ -74,7 +74,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const int* __restrict__ tile_request, const int* __restrict__ tile_start,
                      const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
                      int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale, float softcap,
-                     const __nv_bfloat16* __restrict__ gate, long long gate_stride, int has_sink, float sink_log2,
+                     const __nv_bfloat16* __restrict__ gate, long long gate_stride, int has_sink, float sink_log2, const float* __restrict__ sink_heads,
                      int* status) {
   constexpr int CHUNKS = HD / 8;                      // 16-byte chunks per row
   constexpr int TILE_BYTES = kFlashKeys * HD * 2;
@@ -275,6 +275,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   }
 
   if (has_sink) {   // one more key, without a value, in the denominator (its score in units of log 2)
+    if (sink_heads != nullptr) sink_log2 = sink_heads[head] * 1.4426950408889634f;   // one score per head
     l_lo += fast_exp2(sink_log2 - m_lo);
     l_hi += fast_exp2(sink_log2 - m_hi);
   }
@@ -305,7 +306,7 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
                         const int* tile_request, const int* tile_start, const int* tile_length,
                         const int* positions, int tiles, int heads, int kv_heads, int page_tokens,
                         int num_pages, int window, int chunk, float scale, const void* gate, long long gate_stride,
-                        float softcap, int has_sink, float sink_score, int* status, cudaStream_t stream) {
+                        float softcap, int has_sink, float sink_score, const float* sink_heads, int* status, cudaStream_t stream) {
   const int shared = 4 * kFlashKeys * HD * 2;
   auto kernel = flash_prefill_kernel<HD>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
@@ -315,7 +316,7 @@ static int launch_flash(const void* q, const void* cache, void* out, const int* 
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(cache),
       static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start, tile_length,
       positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, softcap,
-      static_cast<const __nv_bfloat16*>(gate), gate_stride, has_sink, sink_score * 1.4426950408889634f, status);
+      static_cast<const __nv_bfloat16*>(gate), gate_stride, has_sink, sink_score * 1.4426950408889634f, sink_heads, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -338,14 +339,14 @@ MXB_API int mxb_flash_prefill(const void* q, const void* cache, void* out, const
                               const int* tile_length, const int* positions, int tiles, int heads,
                               int kv_heads, int head_dim, int page_tokens, int num_pages, int window, int chunk,
                               float scale, int dtype, const void* gate, long long gate_stride, float softcap,
-                              int has_sink, float sink_score, int* status, cudaStream_t stream) {
+                              int has_sink, float sink_score, const float* sink_heads, int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (!mxb_flash_prefill_supported(head_dim, heads, kv_heads, dtype)) return static_cast<int>(cudaErrorInvalidValue);
   if (head_dim == 64)
     return launch_flash<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                             positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, softcap, has_sink,
-                            sink_score, status, stream);
+                            sink_score, sink_heads, status, stream);
   return launch_flash<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                            positions, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, softcap, has_sink,
-                            sink_score, status, stream);
+                            sink_score, sink_heads, status, stream);
 }

@@ -77,7 +77,7 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const int* __restrict__ tile_length, const int* __restrict__ positions, int heads,
                              int kv_heads, int page_tokens, int num_pages, int window, int chunk, float scale, float softcap,
                              int shared_bytes, float* __restrict__ partial, const __nv_bfloat16* __restrict__ gate,
-                             long long gate_stride, int has_sink, float sink_log2, int* status) {
+                             long long gate_stride, int has_sink, float sink_log2, const float* __restrict__ sink_heads, int* status) {
   using Config = FaConfig<HD>;
   constexpr int MAX_STAGES = Config::kKeyStages;
   constexpr int HALVES = Config::kHalves;
@@ -396,7 +396,8 @@ flash_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __
         *reinterpret_cast<float2*>(dst + part * PART_HD + c + 2) = make_float2(acc[c + 2], acc[c + 3]);
       if (part == 0) { dst[HD] = m; dst[HD + 1] = l; }
     } else if (ok && valid) {
-      if (has_sink) l += fa_exp2(sink_log2 - m);   // one more key, without a value, in the denominator
+      // one more key, without a value, in the denominator: one score for all heads, or one per head
+      if (has_sink) l += fa_exp2((sink_heads != nullptr ? sink_heads[head] * 1.4426950408889634f : sink_log2) - m);
       const float inv = 1.0f / l;
       __nv_bfloat16* dst = out + (static_cast<size_t>(t0 + row) * heads + head) * HD + part * PART_HD;
       if (gate != nullptr) {   // an output gate over the concatenated heads: acc * sigmoid(gate) / l
@@ -446,7 +447,7 @@ __global__ void __launch_bounds__(HD)
 flash_prefill_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                            const int* __restrict__ tile_start, const int* __restrict__ tile_length, int heads,
                            int shares, const __nv_bfloat16* __restrict__ gate, long long gate_stride, int has_sink,
-                           float sink_log2) {
+                           float sink_log2, const float* __restrict__ sink_heads) {
   const int head = blockIdx.x, tile = blockIdx.y, d = threadIdx.x;
   const int t0 = tile_start[tile], n = tile_length[tile];
   for (int row = blockIdx.z; row < n; row += kMergeGroups) {
@@ -469,7 +470,8 @@ flash_prefill_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __r
       value = fmaf(weight, values[s], value);
       sum = fmaf(weight, sums[s], sum);
     }
-    if (has_sink) sum += fa_exp2(sink_log2 - highest);   // one more key, without a value, in the denominator
+    // one more key, without a value, in the denominator: one score for all heads, or one per head
+    if (has_sink) sum += fa_exp2((sink_heads != nullptr ? sink_heads[head] * 1.4426950408889634f : sink_log2) - highest);
     if (gate != nullptr) value *= sigmoid_of(__bfloat162float(gate[(t0 + row) * gate_stride + head * HD + d]));
     out[(static_cast<size_t>(t0 + row) * heads + head) * HD + d] = __float2bfloat16_rn(value / sum);
   }
@@ -480,7 +482,7 @@ static int launch_flash_tc(const void* q, const void* cache, void* out, const in
                            const int* tile_request, const int* tile_start, const int* tile_length,
                            const int* positions, int tokens, int tiles, int heads, int kv_heads, int page_tokens,
                            int num_pages, int window, int chunk, float scale, int key_shares, float* partial,
-                           const void* gate, long long gate_stride, float softcap, int has_sink, float sink_score,
+                           const void* gate, long long gate_stride, float softcap, int has_sink, float sink_score, const float* sink_heads,
                            int* status, cudaStream_t stream) {
   using Config = FaConfig<HD>;
   const float sink_log2 = sink_score * 1.4426950408889634f;
@@ -506,12 +508,12 @@ static int launch_flash_tc(const void* q, const void* cache, void* out, const in
   kernel<<<grid, kFaThreads, shared_bytes, stream>>>(
       map_q, map_cache, static_cast<__nv_bfloat16*>(out), block_tables, max_pages, tile_request, tile_start,
       tile_length, positions, heads, kv_heads, page_tokens, num_pages, window, chunk, scale, softcap, shared_bytes,
-      shared_out ? partial : nullptr, static_cast<const __nv_bfloat16*>(gate), gate_stride, has_sink, sink_log2, status);
+      shared_out ? partial : nullptr, static_cast<const __nv_bfloat16*>(gate), gate_stride, has_sink, sink_log2, sink_heads, status);
   e = cudaGetLastError();
   if (e != cudaSuccess || !shared_out) return static_cast<int>(e);
   flash_prefill_merge_kernel<HD><<<dim3(heads, tiles, kMergeGroups), HD, 0, stream>>>(
       partial, static_cast<__nv_bfloat16*>(out), tile_start, tile_length, heads, key_shares,
-      static_cast<const __nv_bfloat16*>(gate), gate_stride, has_sink, sink_log2);
+      static_cast<const __nv_bfloat16*>(gate), gate_stride, has_sink, sink_log2, sink_heads);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -539,7 +541,7 @@ MXB_API int mxb_flash_prefill_tcgen05(const void* q, const void* cache, void* ou
                                       int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
                                       int window, int chunk, float scale, int dtype, int key_shares, float* partial,
                                       const void* gate, long long gate_stride, float softcap, int has_sink,
-                                      float sink_score, int* status, cudaStream_t stream) {
+                                      float sink_score, const float* sink_heads, int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (key_shares < 1 || key_shares > kMergeShares || (key_shares > 1 && partial == nullptr))
     return static_cast<int>(cudaErrorInvalidValue);
@@ -551,8 +553,8 @@ MXB_API int mxb_flash_prefill_tcgen05(const void* q, const void* cache, void* ou
   if (head_dim == 64)
     return launch_flash_tc<64>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                                positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
-                               key_shares, partial, gate, gate_stride, softcap, has_sink, sink_score, status, stream);
+                               key_shares, partial, gate, gate_stride, softcap, has_sink, sink_score, sink_heads, status, stream);
   return launch_flash_tc<128>(q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length,
                               positions, tokens, tiles, heads, kv_heads, page_tokens, num_pages, window, chunk, scale,
-                              key_shares, partial, gate, gate_stride, softcap, has_sink, sink_score, status, stream);
+                              key_shares, partial, gate, gate_stride, softcap, has_sink, sink_score, sink_heads, status, stream);
 }

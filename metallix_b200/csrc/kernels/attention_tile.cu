@@ -23,7 +23,8 @@
 // make up the output, out being [tokens, heads, value_dim]; the output gate
 // may be one number per (token, head) (`gate_per_head`) instead of one per value;
 // `has_sink` adds a key without a value whose score is `sink_score` to every
-// query's softmax (with score 0: one more in the denominator).
+// query's softmax (with score 0: one more in the denominator); `sink_heads`, when
+// given, holds one such score per query head (float32) and is used instead.
 #include "common.cuh"
 
 namespace mxb {
@@ -41,7 +42,7 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
                             const int* __restrict__ tile_length, const int* __restrict__ positions,
                             int heads, int kv_heads, int head_dim, int page_tokens, int num_pages,
                             int window, int chunk, float scale, const T* __restrict__ gate, long long gate_stride,
-                            int planes, int value_dim, float softcap, int gate_per_head, int has_sink, float sink_score,
+                            int planes, int value_dim, float softcap, int gate_per_head, int has_sink, float sink_score, const float* sink_heads,
                             int* status) {
   extern __shared__ float shared[];
   float* sQ = shared;                                   // [16][head_dim]
@@ -145,7 +146,7 @@ paged_attention_tile_kernel(const T* __restrict__ q, const T* __restrict__ cache
   }
 
   if (row_valid) {
-    const float inv = 1.0f / (has_sink ? l + expf(sink_score - m) : l);
+    const float inv = 1.0f / (has_sink ? l + expf((sink_heads != nullptr ? sink_heads[head] : sink_score) - m) : l);
     T* dst = out + (static_cast<size_t>(t0 + r) * heads + head) * value_dim;
     const T* g = gate != nullptr ? gate + (t0 + r) * gate_stride + static_cast<long long>(head) * (gate_per_head ? 1 : value_dim)
                                  : nullptr;
@@ -165,7 +166,7 @@ static int launch_tile(const void* q, const void* cache, void* out, const int* b
                        const int* tile_length, const int* positions, int tiles, int heads,
                        int kv_heads, int head_dim, int page_tokens, int num_pages, int window, int chunk,
                        float scale, const void* gate, long long gate_stride, int planes, int value_dim, float softcap,
-                       int gate_per_head, int has_sink, float sink_score, int* status, cudaStream_t stream) {
+                       int gate_per_head, int has_sink, float sink_score, const float* sink_heads, int* status, cudaStream_t stream) {
   const size_t shared = sizeof(float) * (static_cast<size_t>(kTileQueries) * head_dim +
                                          static_cast<size_t>(kTileKeys) * (head_dim + 1) +
                                          static_cast<size_t>(kTileKeys) * head_dim +
@@ -180,7 +181,7 @@ static int launch_tile(const void* q, const void* cache, void* out, const int* b
       static_cast<const T*>(q), static_cast<const T*>(cache), static_cast<T*>(out), block_tables,
       max_pages, tile_request, tile_start, tile_length, positions, heads, kv_heads, head_dim,
       page_tokens, num_pages, window, chunk, scale, static_cast<const T*>(gate), gate_stride, planes, value_dim, softcap,
-      gate_per_head, has_sink, sink_score, status);
+      gate_per_head, has_sink, sink_score, sink_heads, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -198,13 +199,13 @@ MXB_API int mxb_paged_attention_tile(const void* q, const void* cache, void* out
                                      int heads, int kv_heads, int head_dim, int page_tokens,
                                      int num_pages, int window, int chunk, float scale, int dtype, const void* gate,
                                      long long gate_stride, int planes, int value_dim, float softcap,
-                                     int gate_per_head, int has_sink, float sink_score, int* status,
+                                     int gate_per_head, int has_sink, float sink_score, const float* sink_heads, int* status,
                                      cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (head_dim <= 0 || head_dim > 576 || heads % kv_heads != 0) return static_cast<int>(cudaErrorInvalidValue);
   if ((planes != 1 && planes != 2) || value_dim <= 0 || value_dim > head_dim) return static_cast<int>(cudaErrorInvalidValue);
 #define ARGS q, cache, out, block_tables, max_pages, tile_request, tile_start, tile_length, positions, \
-             tiles, heads, kv_heads, head_dim, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, planes, value_dim, softcap, gate_per_head, has_sink, sink_score, status, stream
+             tiles, heads, kv_heads, head_dim, page_tokens, num_pages, window, chunk, scale, gate, gate_stride, planes, value_dim, softcap, gate_per_head, has_sink, sink_score, sink_heads, status, stream
 #define DISPATCH(T)                                           \
   if (head_dim <= 16) return launch_tile<T, 2>(ARGS);         \
   if (head_dim <= 32) return launch_tile<T, 4>(ARGS);         \

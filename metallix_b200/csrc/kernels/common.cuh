@@ -70,6 +70,14 @@ __device__ __forceinline__ void prefetch_line(const void* p) { asm volatile("pre
 // sigmoid(gate[token * gate_stride + head * head_dim + d]), in float32.
 __device__ __forceinline__ float sigmoid_of(float g) { return 1.0f / (1.0f + expf(-g)); }
 
+// The activation of a gated feed-forward, act(gate) * up: silu(z) = z / (1 + e^-z), or the tanh form of
+// gelu, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+enum GateActivation : int { kActSilu = 0, kActGeluTanh = 1 };
+__device__ __forceinline__ float gate_activation(float z, int activation) {
+  if (activation == kActGeluTanh) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
+  return __fdividef(z, 1.0f + __expf(-z));
+}
+
 // A cap c on a scaled score ahead of the softmax: s <- c tanh(s / c), which keeps small scores and
 // bounds all of them to (-c, c); c = 0 leaves the score as it is.
 __device__ __forceinline__ float capped_score(float s, float cap) { return cap > 0.0f ? cap * tanhf(s / cap) : s; }

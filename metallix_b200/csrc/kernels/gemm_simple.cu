@@ -65,24 +65,28 @@ gemm_simple_kernel(TOut* __restrict__ c, const TIn* __restrict__ a, const TIn* _
   }
 }
 
-// out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i], float32 inside:
+// out[t, i] = act(gate_up[t, i]) * gate_up[t, inter + i], float32 inside (act: silu, or the tanh form of gelu):
 // sigmoid(g) * g * u as the reference writes it
 // (crates/models/qwen/src/forward.rs:1913-1917).
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter,
-                                size_t count) {
+                                size_t count, int activation) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= count) return;
   const size_t t = i / inter, col = i - t * inter;
   const float g = to_float(gate_up[t * 2 * inter + col]);
   const float u = to_float(gate_up[t * 2 * inter + inter + col]);
+  if (activation == kActGeluTanh) {
+    out[i] = from_float<T>(0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u);
+    return;
+  }
   const float sig = 1.0f / (1.0f + expf(-g));
   out[i] = from_float<T>(sig * g * u);
 }
 
 // Eight bfloat16 values per thread (16-byte loads and stores).
 __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
-                                       int inter, size_t groups) {
+                                       int inter, size_t groups, int activation) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= groups) return;
   const int per_row = inter / 8;
@@ -95,8 +99,14 @@ __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
   for (int j = 0; j < 4; ++j) {
     const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xffff0000u);
     const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xffff0000u);
-    const float r0 = (1.0f / (1.0f + expf(-g0))) * g0 * u0;
-    const float r1 = (1.0f / (1.0f + expf(-g1))) * g1 * u1;
+    float r0, r1;
+    if (activation == kActGeluTanh) {
+      r0 = 0.5f * g0 * (1.0f + tanhf(0.7978845608028654f * (g0 + 0.044715f * g0 * g0 * g0))) * u0;
+      r1 = 0.5f * g1 * (1.0f + tanhf(0.7978845608028654f * (g1 + 0.044715f * g1 * g1 * g1))) * u1;
+    } else {
+      r0 = (1.0f / (1.0f + expf(-g0))) * g0 * u0;
+      r1 = (1.0f / (1.0f + expf(-g1))) * g1 * u1;
+    }
     __nv_bfloat162 packed = __floats2bfloat162_rn(r0, r1);
     ow[j] = *reinterpret_cast<uint32_t*>(&packed);
   }
@@ -122,7 +132,7 @@ MXB_API int mxb_gemm_simple(void* c, int c_dtype, const void* a, const void* w, 
   return static_cast<int>(cudaGetLastError());
 }
 
-MXB_API int mxb_silu_mul(void* out, const void* gate_up, int dtype, long long tokens, int inter,
+MXB_API int mxb_silu_mul(void* out, const void* gate_up, int dtype, long long tokens, int inter, int activation,
                          cudaStream_t stream) {
   const size_t count = static_cast<size_t>(tokens) * inter;
   if (count == 0) return 0;
@@ -130,14 +140,14 @@ MXB_API int mxb_silu_mul(void* out, const void* gate_up, int dtype, long long to
       reinterpret_cast<uintptr_t>(gate_up) % 16 == 0) {
     const size_t groups = count / 8;
     silu_mul_bf16x8_kernel<<<static_cast<unsigned>((groups + 255) / 256), 256, 0, stream>>>(
-        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), inter, groups);
+        static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), inter, groups, activation);
     return static_cast<int>(cudaGetLastError());
   }
   const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
   if (dtype == kF32)
-    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(gate_up), inter, count);
+    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<float*>(out), static_cast<const float*>(gate_up), inter, count, activation);
   else if (dtype == kBF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), inter, count);
+    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(gate_up), inter, count, activation);
   else
     return static_cast<int>(cudaErrorInvalidValue);
   return static_cast<int>(cudaGetLastError());

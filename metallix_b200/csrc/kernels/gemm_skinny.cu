@@ -43,7 +43,7 @@ template <int MB, bool SWIGLU, typename TOut, int WROWS>
 __global__ void __launch_bounds__(kSkinnyThreads)
 gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, int m, int n, int k, long long ldx, long long ldw,
-                   long long ldo, int inter) {
+                   long long ldo, int inter, int activation) {
   constexpr int SETS = SWIGLU ? 2 : 1;
   __shared__ float s_part[kSkinnyWarps][WROWS][MB * 8 + 1];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -180,7 +180,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
       // keep the same rounding points so both paths agree.
       const float gate = to_float(from_float<__nv_bfloat16>(sums[0][item]));
       const float up = to_float(from_float<__nv_bfloat16>(sums[SETS - 1][item]));
-      value = __fdividef(gate, 1.0f + __expf(-gate)) * up;  // the result is rounded to bfloat16 anyway
+      value = gate_activation(gate, activation) * up;  // the result is rounded to bfloat16 anyway
     }
     store_out(out + static_cast<long long>(row_m) * ldo + column, value);
   }
@@ -188,7 +188,7 @@ gemm_skinny_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x,
 
 template <int MB, bool SWIGLU>
 static int launch_skinny(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
-                         long long ldx, long long ldw, long long ldo, int inter, cudaStream_t stream) {
+                         long long ldx, long long ldw, long long ldo, int inter, int activation, cudaStream_t stream) {
   const int columns = SWIGLU ? inter : n;
   // Narrow outputs take 8 rows of W per block so that at least ~2 blocks per SM exist.
   const bool narrow = columns <= 2048;
@@ -196,7 +196,7 @@ static int launch_skinny(void* out, int out_dtype, const void* x, const void* w,
   const unsigned long long streamed = static_cast<unsigned long long>(n) * k * 2;   // the bytes of W
 #define GO(TOUT, WROWS) return static_cast<int>(launch_chained_sized(streamed, gemm_skinny_kernel<MB, SWIGLU, TOUT, WROWS>, grid, \
       dim3(kSkinnyThreads), 0, stream, static_cast<TOUT*>(out), static_cast<const __nv_bfloat16*>(x), \
-      static_cast<const __nv_bfloat16*>(w), m, n, k, ldx, ldw, ldo, inter))
+      static_cast<const __nv_bfloat16*>(w), m, n, k, ldx, ldw, ldo, inter, activation))
   if (out_dtype == kBF16) { if (narrow) GO(__nv_bfloat16, 8); else GO(__nv_bfloat16, 16); }
   else { if (narrow) GO(float, 8); else GO(float, 16); }
 #undef GO
@@ -213,16 +213,17 @@ MXB_API int mxb_gemm_skinny_supported(int m, int n, int k, long long ldx, long l
 }
 
 // swiglu_inter == 0: out[m, n] = x w^T. swiglu_inter == inter > 0: w is
-// [2 * inter, k] (gate rows, then up rows), out is [m, inter].
+// [2 * inter, k] (gate rows, then up rows), out is [m, inter] = act(gate) * up with
+// act chosen by `activation` (see GateActivation).
 MXB_API int mxb_gemm_skinny(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
-                            long long ldx, long long ldw, long long ldo, int swiglu_inter,
+                            long long ldx, long long ldw, long long ldo, int swiglu_inter, int activation,
                             cudaStream_t stream) {
   if (!mxb_gemm_skinny_supported(m, n, k, ldx, ldw)) return static_cast<int>(cudaErrorInvalidValue);
   if (out_dtype != kBF16 && out_dtype != kF32) return static_cast<int>(cudaErrorInvalidValue);
   if (swiglu_inter != 0 && n != 2 * swiglu_inter) return static_cast<int>(cudaErrorInvalidValue);
 #define LAUNCH(MB)                                                                                      \
-  return swiglu_inter ? launch_skinny<MB, true>(out, out_dtype, x, w, m, n, k, ldx, ldw, ldo, swiglu_inter, stream) \
-                      : launch_skinny<MB, false>(out, out_dtype, x, w, m, n, k, ldx, ldw, ldo, 0, stream)
+  return swiglu_inter ? launch_skinny<MB, true>(out, out_dtype, x, w, m, n, k, ldx, ldw, ldo, swiglu_inter, activation, stream) \
+                      : launch_skinny<MB, false>(out, out_dtype, x, w, m, n, k, ldx, ldw, ldo, 0, 0, stream)
   if (m <= 8) { LAUNCH(1); }
   if (m <= 16) { LAUNCH(2); }
   if (m <= 32) { LAUNCH(4); }

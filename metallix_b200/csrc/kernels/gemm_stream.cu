@@ -45,7 +45,7 @@ template <typename TOut> __device__ __forceinline__ void stream_store(TOut* p, f
 template <int MB, bool SWIGLU, typename TOut, int R>
 __global__ void __launch_bounds__(kStreamThreads)
 gemm_stream_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                   int m, int n, int k, long long ldx, long long ldw, long long ldo, int inter, int* status) {
+                   int m, int n, int k, long long ldx, long long ldw, long long ldo, int inter, int activation, int* status) {
   constexpr int SETS = SWIGLU ? 2 : 1;
   constexpr int W_ROWS = SETS * R, X_ROWS = MB * 8;
   extern __shared__ __align__(128) unsigned char stream_shared[];
@@ -161,7 +161,7 @@ gemm_stream_kernel(TOut* __restrict__ out, const __nv_bfloat16* __restrict__ x, 
       // keep the same rounding points so both paths agree.
       const float gate = to_float(from_float<__nv_bfloat16>(sums[0][item]));
       const float up = to_float(from_float<__nv_bfloat16>(sums[SETS - 1][item]));
-      value = __fdividef(gate, 1.0f + __expf(-gate)) * up;  // the result is rounded to bfloat16 anyway
+      value = gate_activation(gate, activation) * up;  // the result is rounded to bfloat16 anyway
     }
     stream_store(out + static_cast<long long>(row_m) * ldo + column, value);
   }
@@ -173,7 +173,7 @@ static size_t stream_shared_bytes(int m_rows, int w_rows, int k) {
 
 template <int MB, bool SWIGLU, typename TOut, int R>
 static int launch_stream_rows(void* out, const void* x, const void* w, int m, int n, int k, long long ldx,
-                              long long ldw, long long ldo, int inter, int* status, cudaStream_t stream) {
+                              long long ldw, long long ldo, int inter, int activation, int* status, cudaStream_t stream) {
   const int columns = SWIGLU ? inter : n;
   const size_t shared = stream_shared_bytes(MB * 8, (SWIGLU ? 2 : 1) * R, k);
   auto kernel = gemm_stream_kernel<MB, SWIGLU, TOut, R>;
@@ -184,7 +184,7 @@ static int launch_stream_rows(void* out, const void* x, const void* w, int m, in
   return static_cast<int>(launch_chained_sized(static_cast<unsigned long long>(n) * k * 2, kernel,
                                                dim3((columns + R - 1) / R), dim3(kStreamThreads), shared, stream,
                                          static_cast<TOut*>(out), static_cast<const __nv_bfloat16*>(x),
-                                         static_cast<const __nv_bfloat16*>(w), m, n, k, ldx, ldw, ldo, inter, status));
+                                         static_cast<const __nv_bfloat16*>(w), m, n, k, ldx, ldw, ldo, inter, activation, status));
 }
 
 // Rows of W per block: 16 where that still leaves about two blocks per SM
@@ -198,9 +198,9 @@ static int stream_rows(int m_rows, int columns, int k, bool swiglu) {
 
 template <int MB, bool SWIGLU>
 static int launch_stream(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
-                         long long ldx, long long ldw, long long ldo, int inter, int* status, cudaStream_t stream) {
+                         long long ldx, long long ldw, long long ldo, int inter, int activation, int* status, cudaStream_t stream) {
   const int rows = stream_rows(MB * 8, SWIGLU ? inter : n, k, SWIGLU);
-#define GO(TOUT, R) return launch_stream_rows<MB, SWIGLU, TOUT, R>(out, x, w, m, n, k, ldx, ldw, ldo, inter, status, stream)
+#define GO(TOUT, R) return launch_stream_rows<MB, SWIGLU, TOUT, R>(out, x, w, m, n, k, ldx, ldw, ldo, inter, activation, status, stream)
   if (out_dtype == kBF16) { if (rows == 16) GO(__nv_bfloat16, 16); else GO(__nv_bfloat16, 8); }
   else { if (rows == 16) GO(float, 16); else GO(float, 8); }
 #undef GO
@@ -220,16 +220,17 @@ MXB_API int mxb_gemm_stream_supported(int m, int n, int k, long long ldx, long l
 }
 
 // swiglu_inter == 0: out[m, n] = x w^T. swiglu_inter == inter > 0: w is
-// [2 * inter, k] (gate rows, then up rows), out is [m, inter].
+// [2 * inter, k] (gate rows, then up rows), out is [m, inter] = act(gate) * up with
+// act chosen by `activation` (see GateActivation).
 MXB_API int mxb_gemm_stream(void* out, int out_dtype, const void* x, const void* w, int m, int n, int k,
-                            long long ldx, long long ldw, long long ldo, int swiglu_inter, int* status,
+                            long long ldx, long long ldw, long long ldo, int swiglu_inter, int activation, int* status,
                             cudaStream_t stream) {
   if (!mxb_gemm_stream_supported(m, n, k, ldx, ldw, swiglu_inter)) return static_cast<int>(cudaErrorInvalidValue);
   if (out_dtype != kBF16 && out_dtype != kF32) return static_cast<int>(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return static_cast<int>(cudaErrorInvalidValue);
 #define LAUNCH(MB)                                                                                                \
-  return swiglu_inter ? launch_stream<MB, true>(out, out_dtype, x, w, m, n, k, ldx, ldw, ldo, swiglu_inter, status, stream) \
-                      : launch_stream<MB, false>(out, out_dtype, x, w, m, n, k, ldx, ldw, ldo, 0, status, stream)
+  return swiglu_inter ? launch_stream<MB, true>(out, out_dtype, x, w, m, n, k, ldx, ldw, ldo, swiglu_inter, activation, status, stream) \
+                      : launch_stream<MB, false>(out, out_dtype, x, w, m, n, k, ldx, ldw, ldo, 0, 0, status, stream)
   if (m <= 8) { LAUNCH(1); }
   LAUNCH(2);
 #undef LAUNCH

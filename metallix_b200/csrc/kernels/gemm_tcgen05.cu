@@ -22,7 +22,9 @@ constexpr int kTcM = 128;     // rows of a tile
 constexpr int kTcK = 64;      // k per stage: 64 bfloat16 = one 128-byte swizzle row
 constexpr int kTcThreads = 192;
 
-enum TcEpilogue : int { kTcStoreBf16 = 0, kTcStoreF32 = 1, kTcSwiGLU = 2, kTcReluSquared = 3 };
+enum TcEpilogue : int { kTcStoreBf16 = 0, kTcStoreF32 = 1, kTcSwiGLU = 2, kTcReluSquared = 3, kTcGeGLU = 4 };
+// the epilogues that take a tile of gate rows beside a tile of up rows: act(gate) * up (silu, or the tanh form of gelu)
+__host__ __device__ constexpr bool tc_gated(int epilogue) { return epilogue == kTcSwiGLU || epilogue == kTcGeGLU; }
 
 template <int BN, int STAGES_> struct TcConfig {
   static constexpr int kStageBytes = (kTcM + BN) * kTcK * 2;
@@ -52,7 +54,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     int group_rows, int* status) {
   using Config = TcConfig<BN, STAGES_>;
   constexpr int STAGES = Config::kStages;
-  constexpr int OUT_COLUMNS = EPI == kTcSwiGLU ? BN / 2 : BN;  // output columns of a tile
+  constexpr int OUT_COLUMNS = tc_gated(EPI) ? BN / 2 : BN;  // output columns of a tile
   extern __shared__ unsigned char tc_shared_raw[];
   __shared__ __align__(8) uint64_t full_barrier[STAGES];
   __shared__ __align__(8) uint64_t empty_barrier[STAGES];
@@ -110,7 +112,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           unsigned char* b_tile = a_tile + kTcM * kTcK * 2;
           barrier_arrive_expect(&full_barrier[stage], Config::kStageBytes);
           tma_load_2d(a_tile, &map_a, kb * kTcK, m0, &full_barrier[stage]);
-          if (EPI == kTcSwiGLU) {
+          if (tc_gated(EPI)) {
             tma_load_2d(b_tile, &map_b, kb * kTcK, n0, &full_barrier[stage]);                            // gate rows
             tma_load_2d(b_tile + (BN / 2) * kTcK * 2, &map_b, kb * kTcK, n + n0, &full_barrier[stage]);  // up rows
           } else {
@@ -167,7 +169,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t acc[32];
         tc_load_32(tmem_row + c, acc);
         float values[32];
-        if (EPI == kTcSwiGLU) {
+        if (tc_gated(EPI)) {
           uint32_t up[32];
           tc_load_32(tmem_row + BN / 2 + c, up);
 #pragma unroll
@@ -175,7 +177,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // gate and up take the rounding to bfloat16 they would get on their way through memory
             const float gate = to_float(from_float<__nv_bfloat16>(__uint_as_float(acc[i])));
             const float u = to_float(from_float<__nv_bfloat16>(__uint_as_float(up[i])));
-            values[i] = __fdividef(gate, 1.0f + __expf(-gate)) * u;  // the result is rounded to bfloat16 anyway
+            values[i] = gate_activation(gate, EPI == kTcGeGLU ? kActGeluTanh : kActSilu) * u;  // rounded to bfloat16 anyway
           }
         } else if (EPI == kTcReluSquared) {
 #pragma unroll
@@ -249,7 +251,7 @@ static int launch_tc_staged(const CUtensorMap& map_a, const CUtensorMap& map_b, 
   auto kernel = gemm_tcgen05_kernel<BN, EPI, STAGES_>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config::kSharedBytes);
   if (e != cudaSuccess) return static_cast<int>(e);
-  constexpr int out_columns = EPI == kTcSwiGLU ? BN / 2 : BN;
+  constexpr int out_columns = tc_gated(EPI) ? BN / 2 : BN;
   const int tiles = ((n + out_columns - 1) / out_columns) * ((m + kTcM - 1) / kTcM);
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -287,16 +289,17 @@ MXB_API int mxb_gemm_tcgen05_supported(int m, int n, int k, long long lda, long 
 }
 
 // epilogue: 0 bfloat16 out[m, n], 1 float32 out[m, n], 2 SwiGLU: w is
-// [2 * n, k] (gate rows, then up rows) and out is bfloat16 [m, n].
+// [2 * n, k] (gate rows, then up rows) and out is bfloat16 [m, n]; 4 the same
+// with the tanh form of gelu in place of silu.
 MXB_API int mxb_gemm_tcgen05(void* out, const void* a, const void* w, int m, int n, int k, long long lda,
                              long long ldw, long long ldo, int epilogue, int* status, cudaStream_t stream) {
   if (!mxb_gemm_tcgen05_supported(m, n, k, lda, ldw)) return static_cast<int>(cudaErrorInvalidValue);
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return static_cast<int>(cudaErrorInvalidValue);
-  const int w_rows = epilogue == kTcSwiGLU ? 2 * n : n;
+  const int w_rows = tc_gated(epilogue) ? 2 * n : n;
   // Narrow outputs take narrower tiles so that the grid still covers the GPU.
   const int m_tiles = (m + kTcM - 1) / kTcM;
   int bn = 256;
-  if (epilogue == kTcSwiGLU) {
+  if (tc_gated(epilogue)) {
     // A SwiGLU tile of width bn holds bn / 2 gate and bn / 2 up rows. Timed
     // on [m, 1024] x [6144, 1024]: up to 128 rows 64 is fastest (10 against 14
     // us), at 256 rows 128 (12 against 15), from 512 rows on 256.
@@ -308,13 +311,18 @@ MXB_API int mxb_gemm_tcgen05(void* out, const void* a, const void* w, int m, int
   }
   if (g_tc_bn != 0) bn = g_tc_bn;
   CUtensorMap map_a, map_b;
-  const int b_box = epilogue == kTcSwiGLU ? bn / 2 : bn;
+  const int b_box = tc_gated(epilogue) ? bn / 2 : bn;
   if (!make_map(&map_a, a, m, k, lda, kTcM) || !make_map(&map_b, w, w_rows, k, ldw, b_box))
     return static_cast<int>(cudaErrorInvalidValue);
   if (epilogue == kTcSwiGLU) {
     if (bn == 256) return launch_tc<256, kTcSwiGLU>(map_a, map_b, out, m, n, k, ldo, status, stream);
     if (bn == 128) return launch_tc<128, kTcSwiGLU>(map_a, map_b, out, m, n, k, ldo, status, stream);
     return launch_tc<64, kTcSwiGLU>(map_a, map_b, out, m, n, k, ldo, status, stream);
+  }
+  if (epilogue == kTcGeGLU) {
+    if (bn == 256) return launch_tc<256, kTcGeGLU>(map_a, map_b, out, m, n, k, ldo, status, stream);
+    if (bn == 128) return launch_tc<128, kTcGeGLU>(map_a, map_b, out, m, n, k, ldo, status, stream);
+    return launch_tc<64, kTcGeGLU>(map_a, map_b, out, m, n, k, ldo, status, stream);
   }
   if (epilogue == kTcStoreF32) {
     if (bn == 256) return launch_tc<256, kTcStoreF32>(map_a, map_b, out, m, n, k, ldo, status, stream);
@@ -332,7 +340,9 @@ MXB_API int mxb_gemm_tcgen05(void* out, const void* a, const void* w, int m, int
 // [group_rows, k] matrix per group; row tile i of a meets matrix
 // tile_group[i] (device memory, m / 128 rounded up entries; negative: the
 // tile is left out); out is [m, n] with n <= group_rows. epilogue: 1 float32,
-// 3 bfloat16 max(c, 0)^2, 0 bfloat16.
+// 3 bfloat16 max(c, 0)^2, 0 bfloat16, 2 SwiGLU: every group's matrix is
+// [2 * n, k], its gate rows and then its up rows (group_rows = 2 n), and out is
+// bfloat16 silu(gate) * up.
 MXB_API int mxb_gemm_tcgen05_grouped(void* out, const void* a, const void* w, const int* tile_group, int m, int n,
                                      int k, int groups, int group_rows, long long lda, long long ldw, long long ldo,
                                      int epilogue, int* status, cudaStream_t stream) {
@@ -341,9 +351,12 @@ MXB_API int mxb_gemm_tcgen05_grouped(void* out, const void* a, const void* w, co
   if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return static_cast<int>(cudaErrorInvalidValue);
   const long long w_rows = static_cast<long long>(groups) * group_rows;
   if (w_rows > 0x7fffffffLL) return static_cast<int>(cudaErrorInvalidValue);
-  const int bn = n > 128 ? 256 : (n > 64 ? 128 : 64);
+  if (epilogue == kTcSwiGLU && group_rows != 2 * n) return static_cast<int>(cudaErrorInvalidValue);
+  // a gated tile of width bn holds bn / 2 gate and bn / 2 up rows
+  const int bn = epilogue == kTcSwiGLU ? (n > 64 ? 256 : (n > 32 ? 128 : 64)) : (n > 128 ? 256 : (n > 64 ? 128 : 64));
   CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, a, m, k, lda, kTcM) || !make_map(&map_b, w, static_cast<int>(w_rows), k, ldw, bn))
+  if (!make_map(&map_a, a, m, k, lda, kTcM) ||
+      !make_map(&map_b, w, static_cast<int>(w_rows), k, ldw, epilogue == kTcSwiGLU ? bn / 2 : bn))
     return static_cast<int>(cudaErrorInvalidValue);
 #define GROUPED(EPI)                                                                                             \
   if (bn == 256) return launch_tc<256, EPI>(map_a, map_b, out, m, n, k, ldo, status, stream, tile_group, group_rows); \
@@ -352,6 +365,7 @@ MXB_API int mxb_gemm_tcgen05_grouped(void* out, const void* a, const void* w, co
   if (epilogue == kTcStoreF32) { GROUPED(kTcStoreF32) }
   if (epilogue == kTcReluSquared) { GROUPED(kTcReluSquared) }
   if (epilogue == kTcStoreBf16) { GROUPED(kTcStoreBf16) }
+  if (epilogue == kTcSwiGLU) { GROUPED(kTcSwiGLU) }
 #undef GROUPED
   return static_cast<int>(cudaErrorInvalidValue);
 }

@@ -1,7 +1,10 @@
 // A feed-forward made of many small experts of which every token uses a few.
 //
 // Router (float32 throughout): s = softmax(z) over all R = experts + identity
-// outputs; the `top` outputs with the largest s + correction are chosen (ties
+// outputs (or, as a switch, s = sigmoid(z) for each output on its own; the
+// outputs may also form equal groups of neighbours of which only the best few,
+// by the sum of a group's two largest s + correction, can be chosen from; and
+// the weights may be multiplied by a constant); the `top` outputs with the largest s + correction are chosen (ties
 // go to the lower index); their weights are their s, divided by the sum of
 // the chosen s (+ 1e-20). The sum s + correction is formed and compared in
 // double precision: where the correction is the same for several outputs and
@@ -37,7 +40,8 @@ constexpr int kRouteThreads = 128;   // four tokens a block, a warp each
 __global__ void __launch_bounds__(kRouteThreads)
 route_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ chosen,
              float* __restrict__ weights, float* __restrict__ dense, float* __restrict__ identity_weight,
-             int tokens, int outputs, int experts, int top) {
+             int tokens, int outputs, int experts, int top, int sigmoid_scores, int group_count, int group_keep,
+             float weight_scale, long long ld) {
   extern __shared__ double shared[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * (kRouteThreads / 32) + warp;
@@ -45,24 +49,70 @@ route_kernel(const float* __restrict__ logits, const float* __restrict__ correct
   double* choice = reinterpret_cast<double*>(shared) + static_cast<size_t>(warp) * outputs;   // s + correction, minus infinity once taken
   float* score = reinterpret_cast<float*>(reinterpret_cast<double*>(shared) + static_cast<size_t>(kRouteThreads / 32) * outputs) +
                  static_cast<size_t>(warp) * outputs;                                        // s
-  const float* z = logits + static_cast<size_t>(t) * outputs;
-  float peak = -INFINITY;
-  for (int r = lane; r < outputs; r += 32) peak = fmaxf(peak, z[r]);
-  peak = warp_max(peak);
-  float total = 0.0f;
-  for (int r = lane; r < outputs; r += 32) {
-    const float e = expf(z[r] - peak);
-    score[r] = e;
-    total += e;
-  }
-  total = warp_sum(total);
-  for (int r = lane; r < outputs; r += 32) {
-    const float s = score[r] / total;
-    score[r] = s;
-    choice[r] = static_cast<double>(s) + static_cast<double>(correction[r]);
+  const float* z = logits + static_cast<long long>(t) * ld;   // rows may be further apart than they are long
+  if (sigmoid_scores) {   // every output's score on its own: s = 1 / (1 + e^-z)
+    for (int r = lane; r < outputs; r += 32) {
+      const float s = 1.0f / (1.0f + expf(-z[r]));
+      score[r] = s;
+      choice[r] = static_cast<double>(s) + static_cast<double>(correction[r]);
+    }
+  } else {
+    float peak = -INFINITY;
+    for (int r = lane; r < outputs; r += 32) peak = fmaxf(peak, z[r]);
+    peak = warp_max(peak);
+    float total = 0.0f;
+    for (int r = lane; r < outputs; r += 32) {
+      const float e = expf(z[r] - peak);
+      score[r] = e;
+      total += e;
+    }
+    total = warp_sum(total);
+    for (int r = lane; r < outputs; r += 32) {
+      const float s = score[r] / total;
+      score[r] = s;
+      choice[r] = static_cast<double>(s) + static_cast<double>(correction[r]);
+    }
   }
   for (int e = lane; e < experts; e += 32) dense[static_cast<size_t>(t) * experts + e] = 0.0f;
   __syncwarp();
+  if (group_count > 1 && group_keep < group_count) {
+    // Outputs form group_count equal groups of neighbours; a group's score is the sum of its two largest
+    // s + correction (of its only one, where a group is a single output); outside the group_keep best groups
+    // (ties to the lower index) nothing can be chosen: those outputs count as minus infinity.
+    double* group_score = reinterpret_cast<double*>(score + static_cast<size_t>(kRouteThreads / 32 - warp) * outputs) +
+                          static_cast<size_t>(warp) * outputs;
+    const int size = outputs / group_count;
+    for (int g = lane; g < group_count; g += 32) {
+      double best = -INFINITY, second = -INFINITY;
+      for (int i = 0; i < size; ++i) {
+        const double v = choice[g * size + i];
+        if (v > best) { second = best; best = v; }
+        else if (v > second) second = v;
+      }
+      group_score[g] = size > 1 ? best + second : best;
+    }
+    __syncwarp();
+    for (int k = 0; k < group_keep; ++k) {
+      double best = -INFINITY;
+      int where = 0x7fffffff;
+      for (int g = lane; g < group_count; g += 32) {
+        const double v = group_score[g];
+        if (v > best) { best = v; where = g; }
+      }
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        const double other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const int other_where = __shfl_xor_sync(0xffffffffu, where, offset);
+        if (other > best || (other == best && other_where < where)) { best = other; where = other_where; }
+      }
+      if (where >= group_count) break;   // nothing comparable left
+      if (lane == 0) group_score[where] = nan("");   // kept: no comparison picks it again
+      __syncwarp();
+    }
+    for (int r = lane; r < outputs; r += 32)
+      if (!isnan(group_score[r / size])) choice[r] = -INFINITY;
+    __syncwarp();
+  }
   float picked_sum = 0.0f;
   for (int k = 0; k < top; ++k) {
     double best = -INFINITY;
@@ -85,7 +135,7 @@ route_kernel(const float* __restrict__ logits, const float* __restrict__ correct
     picked_sum += score[where];
     __syncwarp();
   }
-  const float scale = 1.0f / (picked_sum + 1e-20f);
+  const float scale = weight_scale / (picked_sum + 1e-20f);
   if (lane == 0) {
     float on_identity = 0.0f;
     for (int k = 0; k < top; ++k) {
@@ -107,6 +157,17 @@ __global__ void add_identity_kernel(float* __restrict__ y, const T* __restrict__
   if (index >= total) return;
   const float w = identity_weight[index / hidden];
   if (w != 0.0f) y[index] = fmaf(w, to_float(h[index]), y[index]);
+}
+
+// y[t, :] += sigmoid(gate[t * ldg]) * x[t, :]   (y float32): an expert that every token uses, behind a gate of one
+// number per token
+template <typename T>
+__global__ void add_gated_rows_kernel(float* __restrict__ y, const T* __restrict__ x, const float* __restrict__ gate,
+                                      long long ldg, long long total, int hidden) {
+  const long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (index >= total) return;
+  const float g = gate[(index / hidden) * ldg];
+  y[index] = fmaf(1.0f / (1.0f + expf(-g)), to_float(x[index]), y[index]);
 }
 
 constexpr int kGroupTile = 128;      // rows of a tile of the grouped products
@@ -219,17 +280,27 @@ __device__ __forceinline__ float dot_rows(const T* __restrict__ row, const U* __
 
 constexpr int kRoutedThreads = 256;   // eight warps, a row of a weight each
 
-// act[(t, k), f] = relu(W_up[e * ff + f, :] . h[t, :])^2 * weight[t, k] for e = chosen[t, k] < experts
+// act[(t, k), f] = relu(W_up[e * ff + f, :] . h[t, :])^2 * weight[t, k] for e = chosen[t, k] < experts; or, `gated`,
+// with an expert's matrix [2 * ff, hidden] holding gate rows and then up rows,
+// silu(W_gate[f, :] . h) * (W_up[f, :] . h) * weight
 template <typename T>
 __global__ void __launch_bounds__(kRoutedThreads)
 routed_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ chosen,
-                 const float* __restrict__ weights, float* __restrict__ act, int hidden, int experts, int ff, int top) {
+                 const float* __restrict__ weights, float* __restrict__ act, int hidden, int experts, int ff, int top,
+                 int gated) {
   const int pair = blockIdx.x;                    // token * top + k
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f = blockIdx.y * (kRoutedThreads / 32) + warp;
   const int e = chosen[pair];
   if (f >= ff || e >= experts || e < 0) return;
   const T* x = h + static_cast<size_t>(pair / top) * hidden;
+  if (gated) {
+    const T* gate_row = w_up + (static_cast<size_t>(e) * 2 * ff + f) * hidden;
+    const float gate = warp_sum(dot_rows(gate_row, x, hidden, lane));
+    const float up = warp_sum(dot_rows(gate_row + static_cast<size_t>(ff) * hidden, x, hidden, lane));
+    if (lane == 0) act[static_cast<size_t>(pair) * ff + f] = gate / (1.0f + expf(-gate)) * up * weights[pair];
+    return;
+  }
   const T* row = w_up + (static_cast<size_t>(e) * ff + f) * hidden;
   float sum = dot_rows(row, x, hidden, lane);
   sum = warp_sum(sum);
@@ -271,16 +342,24 @@ using namespace mxb;
 
 // logits: float32 [tokens, outputs]; correction: float32 [outputs]; chosen: int32 [tokens, top];
 // weights: float32 [tokens, top]; dense: float32 [tokens, experts]; identity_weight: float32 [tokens].
+// sigmoid_scores: s = sigmoid(z) instead of softmax(z). group_count > 1: the outputs form that many equal groups of
+// neighbours, and only outputs of the group_keep best groups can be chosen. weight_scale multiplies the weights.
 MXB_API int mxb_route_experts(const float* logits, const float* correction, int* chosen, float* weights, float* dense,
                               float* identity_weight, int tokens, int outputs, int experts, int top,
-                              cudaStream_t stream) {
+                              int sigmoid_scores, int group_count, int group_keep, float weight_scale,
+                              long long ld, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (outputs <= 0 || experts < 0 || experts > outputs || top <= 0 || top > outputs)
     return static_cast<int>(cudaErrorInvalidValue);
-  const size_t shared = (sizeof(float) + sizeof(double)) * outputs * (kRouteThreads / 32);
+  if (group_count > 1 && (outputs % group_count != 0 || group_keep < 1 || group_keep > group_count ||
+                          static_cast<long long>(group_keep) * (outputs / group_count) < top))
+    return static_cast<int>(cudaErrorInvalidValue);
+  // per warp: s + correction (double), s (float) and, with groups, the groups' scores (double)
+  const size_t shared = (sizeof(float) + (group_count > 1 ? 2 : 1) * sizeof(double)) * outputs * (kRouteThreads / 32);
   if (shared > 48 * 1024) return static_cast<int>(cudaErrorInvalidValue);
   route_kernel<<<ceil_div(tokens, kRouteThreads / 32), kRouteThreads, shared, stream>>>(
-      logits, correction, chosen, weights, dense, identity_weight, tokens, outputs, experts, top);
+      logits, correction, chosen, weights, dense, identity_weight, tokens, outputs, experts, top, sigmoid_scores,
+      group_count, group_keep, weight_scale, ld < outputs ? outputs : ld);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -299,30 +378,47 @@ MXB_API int mxb_experts_add_identity(float* y, const void* h, const float* ident
   return static_cast<int>(cudaGetLastError());
 }
 
-// h: [tokens, hidden]; w_up: [experts * ff, hidden]; w_down: [experts * hidden, ff]; act: float32 scratch
-// [tokens * top, ff]; y: float32 [tokens, hidden].
+// h: [tokens, hidden]; w_up: [experts * ff, hidden] (gated: [experts * 2 * ff, hidden], every expert's gate rows
+// and then its up rows, the activation silu instead of relu^2); w_down: [experts * hidden, ff]; act: float32
+// scratch [tokens * top, ff]; y: float32 [tokens, hidden].
 MXB_API int mxb_experts_routed(const void* h, const void* w_up, const void* w_down, const int* chosen,
                                const float* weights, float* act, float* y, int tokens, int hidden, int experts, int ff,
-                               int top, int dtype, cudaStream_t stream) {
+                               int top, int dtype, int gated, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (hidden <= 0 || ff <= 0 || top <= 0) return static_cast<int>(cudaErrorInvalidValue);
   const int per_block = kRoutedThreads / 32;
   dim3 up_grid(tokens * top, ceil_div(ff, per_block)), down_grid(tokens, ceil_div(hidden, per_block));
   if (dtype == kF32) {
     routed_up_kernel<float><<<up_grid, kRoutedThreads, 0, stream>>>(
-        static_cast<const float*>(h), static_cast<const float*>(w_up), chosen, weights, act, hidden, experts, ff, top);
+        static_cast<const float*>(h), static_cast<const float*>(w_up), chosen, weights, act, hidden, experts, ff, top, gated);
     routed_down_kernel<float><<<down_grid, kRoutedThreads, 0, stream>>>(
         act, static_cast<const float*>(w_down), static_cast<const float*>(h), chosen, weights, y, hidden, experts, ff, top);
   } else if (dtype == kBF16) {
     routed_up_kernel<__nv_bfloat16><<<up_grid, kRoutedThreads, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(w_up), chosen, weights, act, hidden,
-        experts, ff, top);
+        experts, ff, top, gated);
     routed_down_kernel<__nv_bfloat16><<<down_grid, kRoutedThreads, 0, stream>>>(
         act, static_cast<const __nv_bfloat16*>(w_down), static_cast<const __nv_bfloat16*>(h), chosen, weights, y,
         hidden, experts, ff, top);
   } else {
     return static_cast<int>(cudaErrorInvalidValue);
   }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// y: float32 [tokens, hidden], in place; x: [tokens, hidden]; gate: float32, one value per token, ldg apart.
+MXB_API int mxb_add_gated_rows(float* y, const void* x, const float* gate, long long ldg, int tokens, int hidden,
+                               int dtype, cudaStream_t stream) {
+  const long long total = static_cast<long long>(tokens) * hidden;
+  if (total <= 0) return 0;
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  if (dtype == kF32)
+    add_gated_rows_kernel<float><<<blocks, 256, 0, stream>>>(y, static_cast<const float*>(x), gate, ldg, total, hidden);
+  else if (dtype == kBF16)
+    add_gated_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(y, static_cast<const __nv_bfloat16*>(x), gate, ldg,
+                                                                    total, hidden);
+  else
+    return static_cast<int>(cudaErrorInvalidValue);
   return static_cast<int>(cudaGetLastError());
 }
 

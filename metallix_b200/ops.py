@@ -36,18 +36,24 @@ _SIGNATURES = {
     "mxb_qk_norm_rope_cache": [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, _P, _P, _P, _P,
                                _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P],
     "mxb_paged_attention_tile": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
-                                 _F, _I, _P, _L, _I, _I, _F, _I, _I, _F, _P, _P],
+                                 _F, _I, _P, _L, _I, _I, _F, _I, _I, _F, _P, _P, _P],
     "mxb_short_conv": [_P, _L, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "mxb_selective_scan": [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                            _I, _P, _P],
-    "mxb_route_experts": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "mxb_route_experts": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _L, _P],
     "mxb_expert_rows": [_P, _P, _P, _I, _I, _I, _P],
     "mxb_expert_rows_tile": [],
     "mxb_expert_rows_experts": [],
     "mxb_expert_gather_rows": [_P, _P, _P, _I, _I, _I, _I, _P],
     "mxb_expert_combine_rows": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "mxb_experts_add_identity": [_P, _P, _P, _I, _I, _I, _P],
-    "mxb_experts_routed": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "mxb_experts_routed": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "mxb_add_gated_rows": [_P, _P, _P, _L, _I, _I, _I, _P],
+    "mxb_pair_add_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "mxb_add_bias": [_P, _L, _I, _P, _P, _L, _I, _I, _I, _P],
+    "mxb_delta_rule_max_dim": [],
+    "mxb_delta_rule": [_P, _L, _I, _I, _I, _P, _L, _I, _P, _L, _P, _P, _P, _L, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                       _I, _P, _P],
     "mxb_add_cast": [_P, _P, _I, _P, _I, _L, _P],
     "mxb_gelu_gate_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "mxb_stream_mix": [_P, _P, _P, _L, _L, _F, _F, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
@@ -62,33 +68,33 @@ _SIGNATURES = {
     "mxb_rotate_into": [_P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P, _I, _I, _P, _P],
     "mxb_relu_squared": [_P, _P, _L, _I, _P],
     "mxb_paged_attention_decode": [_P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                                   _F, _I, _P, _L, _F, _I, _F, _P, _P],
+                                   _F, _I, _P, _L, _F, _I, _F, _P, _P, _P],
     "mxb_postnorm_add_rmsnorm": [_P, _P, _I, _I, _P, _F, _P, _I, _P, _F, _I, _I, _P],
     "mxb_sigmoid_gate": [_P, _P, _P, _L, _L, _L, _I, _I, _I, _P],
     "mxb_softcap": [_P, _F, _L, _P],
     "mxb_paged_attention_decode_supported": [_I, _I, _I, _I],
     "mxb_paged_attention_decode_project_supported": [_I, _I, _I, _I, _I, _P, _L],
     "mxb_paged_attention_decode_project": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I,
-                                           _F, _P, _L, _I, _P, _P, _L, _F, _I, _F, _P, _P],
+                                           _F, _P, _L, _I, _P, _P, _L, _F, _I, _F, _P, _P, _P],
     "mxb_paged_attention_split_keys": [],
     "mxb_set_decode_resident_blocks": [_I, _I],
     "mxb_flash_prefill": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _L, _F, _I, _F,
-                          _P, _P],
+                          _P, _P, _P],
     "mxb_flash_prefill_supported": [_I, _I, _I, _I],
     "mxb_flash_prefill_tile": [],
     "mxb_flash_prefill_tcgen05": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P,
-                                  _P, _L, _F, _I, _F, _P, _P],
+                                  _P, _L, _F, _I, _F, _P, _P, _P],
     "mxb_flash_prefill_tcgen05_supported": [_I, _I, _I, _I, _I],
     "mxb_flash_prefill_tcgen05_tile": [],
     "mxb_gemm_simple": [_P, _I, _P, _P, _I, _I, _I, _I, _L, _L, _L, _P],
-    "mxb_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P],
+    "mxb_gemm_skinny": [_P, _I, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _P],
     "mxb_gemm_skinny_supported": [_I, _I, _I, _L, _L],
-    "mxb_gemm_stream": [_P, _I, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P, _P],
+    "mxb_gemm_stream": [_P, _I, _P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _P, _P],
     "mxb_gemm_stream_supported": [_I, _I, _I, _L, _L, _I],
     "mxb_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _L, _L, _L, _I, _P, _P],
     "mxb_gemm_tcgen05_supported": [_I, _I, _I, _L, _L],
     "mxb_gemm_tcgen05_grouped": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _P, _P],
-    "mxb_silu_mul": [_P, _P, _I, _L, _I, _P],
+    "mxb_silu_mul": [_P, _P, _I, _L, _I, _I, _P],
     "mxb_argmax": [_P, _L, _I, _I, _P, _P, _P, _P],
     "mxb_argmax_pieces": [_I, _I],
     "mxb_sample_icdf": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _P],
@@ -335,6 +341,60 @@ def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return x
 
 
+def pair_add_rmsnorm(x: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], scale: float,
+                     weight: Optional[torch.Tensor], second_weight: Optional[torch.Tensor], eps: float,
+                     out_dtype: torch.dtype, rows_index: Optional[torch.Tensor] = None):
+    """x += scale * (a + b) in float32 (in place; ``a`` and ``b`` are optional,
+    each float32 or bfloat16), then RMSNorm(x) * weight and, with
+    ``second_weight``, RMSNorm(x) * second_weight from the same pass over the
+    row: what a layer needs whose two sublayers read the same input. Returns
+    the one result, or the two as a pair; None without ``weight`` (the sum
+    alone). ``rows_index`` picks rows of x (then nothing is added)."""
+    _check(x, "x", (torch.float32,), 2)
+    size = x.shape[1]
+    for name, delta in (("a", a), ("b", b)):
+        if delta is not None:
+            _check(delta, name, tuple(_CODES), 2)
+            _need(delta.shape == x.shape, f"{name} and x differ in shape")
+    rows = x.shape[0]
+    if rows_index is not None:
+        _check(rows_index, "rows_index", (torch.int32,), 1)
+        _need(a is None and b is None, "rows are picked only where nothing is added")
+        rows = rows_index.numel()
+    first = second = None
+    if weight is not None:
+        _check(weight, "weight", (torch.float32,), 1)
+        _need(weight.numel() == size, "weight has the wrong size")
+        first = torch.empty((rows, size), dtype=out_dtype, device=x.device)
+        if second_weight is not None:
+            _check(second_weight, "second_weight", (torch.float32,), 1)
+            _need(second_weight.numel() == size, "second_weight has the wrong size")
+            second = torch.empty((rows, size), dtype=out_dtype, device=x.device)
+    else:
+        _need(second_weight is None, "a second weight without a first")
+    _need(out_dtype in _CODES, "out_dtype must be float32 or bfloat16")
+    _call("mxb_pair_add_rmsnorm", x.data_ptr(), _ptr(a), _CODES[a.dtype] if a is not None else F32, _ptr(b),
+          _CODES[b.dtype] if b is not None else F32, float(scale), _ptr(weight), _ptr(second_weight), _ptr(first),
+          _ptr(second), _CODES[out_dtype], _ptr(rows_index), rows, size, float(eps), _stream())
+    if weight is None:
+        return None
+    return (first, second) if second_weight is not None else first
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """x + bias over the last axis, for x ``[tokens, width]`` float32 (a product's
+    unrounded result) or already of ``out_dtype``; the sum is float32 and is
+    rounded once. Rows of x may be strided."""
+    _need(x.is_cuda and x.dim() == 2 and x.stride(1) == 1 and x.dtype in _CODES, "x must be [tokens, width]")
+    _check(bias, "bias", (torch.float32,), 1)
+    _need(bias.numel() == x.shape[1], "one bias value per column")
+    _need(out_dtype in _CODES and (x.dtype == torch.float32 or x.dtype == out_dtype), "x must be float32 or of out_dtype")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _call("mxb_add_bias", x.data_ptr(), x.stride(0), _CODES[x.dtype], bias.data_ptr(), out.data_ptr(), out.stride(0),
+          _CODES[out_dtype], x.shape[0], x.shape[1], _stream())
+    return out
+
+
 def postnorm_add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, post_weight: torch.Tensor, post_eps: float,
                          next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
                          out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
@@ -559,25 +619,38 @@ def selective_scan(x: torch.Tensor, step: torch.Tensor, step_bias: torch.Tensor,
 ROUTER_OUTPUTS = 1024   # the most router outputs the routing kernel keeps in shared memory
 
 
-def route_experts(logits: torch.Tensor, correction: torch.Tensor, experts: int, top: int):
-    """Softmax over all router outputs, the ``top`` largest score + correction
-    chosen, weights = the chosen scores over their sum. Returns (chosen int32
+def route_experts(logits: torch.Tensor, correction: torch.Tensor, experts: int, top: int, scores: str = "softmax",
+                  groups: Optional[tuple] = None, scale: float = 1.0):
+    """Scores over all router outputs (``scores``: "softmax" over the row, or
+    "sigmoid" of each logit on its own), the ``top`` largest score + correction
+    chosen, weights = the chosen scores over their sum, times ``scale``.
+    ``groups`` = (count, keep): the outputs form ``count`` equal groups of
+    neighbours and only outputs of the ``keep`` groups with the largest sum of
+    their two largest score + correction can be chosen. ``logits`` is float32
+    ``[tokens, outputs]`` whose rows may be strided. Returns (chosen int32
     ``[tokens, top]``, weights float32 ``[tokens, top]``, dense float32
     ``[tokens, experts]`` with each real expert's weight or zero, float32
     ``[tokens]`` weight that fell on the outputs from ``experts`` on, which
     stand for experts that return their input)."""
-    _check(logits, "logits", (torch.float32,), 2)
+    _need(logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1,
+          "logits must be float32 [tokens, outputs] with unit column stride")
     _check(correction, "correction", (torch.float32,), 1)
     tokens, outputs = logits.shape
     _need(correction.numel() == outputs and 0 <= experts <= outputs and 0 < top <= outputs
           and outputs <= ROUTER_OUTPUTS, "the router's sizes do not fit")
+    _need(scores in ("softmax", "sigmoid"), f"unknown scores {scores!r}")
+    count, keep = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+    if count > 1:
+        _need(outputs % count == 0 and 1 <= keep <= count and keep * (outputs // count) >= top
+              and outputs <= ROUTER_OUTPUTS // 2, "the router's groups do not fit")
     device = logits.device
     chosen = torch.empty((tokens, top), dtype=torch.int32, device=device)
     weights = torch.empty((tokens, top), dtype=torch.float32, device=device)
     dense = torch.empty((tokens, experts), dtype=torch.float32, device=device)
     on_identity = torch.empty((tokens,), dtype=torch.float32, device=device)
     _call("mxb_route_experts", logits.data_ptr(), correction.data_ptr(), chosen.data_ptr(), weights.data_ptr(),
-          dense.data_ptr(), on_identity.data_ptr(), tokens, outputs, experts, top, _stream())
+          dense.data_ptr(), on_identity.data_ptr(), tokens, outputs, experts, top, 1 if scores == "sigmoid" else 0,
+          count, keep, float(scale), logits.stride(0), _stream())
     return chosen, weights, dense, on_identity
 
 
@@ -644,12 +717,14 @@ def experts_add_identity(y: torch.Tensor, h: torch.Tensor, on_identity: torch.Te
 
 
 def experts_routed(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor,
-                   weights: torch.Tensor, experts: int, ff: int) -> torch.Tensor:
+                   weights: torch.Tensor, experts: int, ff: int, gated: bool = False) -> torch.Tensor:
     """sum_k weight[t, k] W_down[e] relu(W_up[e] h_t)^2 over a token's chosen
     experts e = chosen[t, k] < experts, plus h_t times the weights of chosen
     indices from ``experts`` on; float32 ``[tokens, hidden]``. Only the chosen
     experts' weights are read. w_up ``[experts * ff, hidden]``, w_down
-    ``[experts * hidden, ff]``."""
+    ``[experts * hidden, ff]``. ``gated``: an expert is W_down (silu(W_gate h) *
+    (W_up h)) and w_up holds, expert by expert, its gate rows and then its up
+    rows, ``[experts * 2 * ff, hidden]``."""
     dtype = h.dtype
     _check(h, "h", tuple(_CODES), 2)
     _check(w_up, "w_up", (dtype,), 2)
@@ -659,12 +734,26 @@ def experts_routed(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ch
     tokens, hidden = h.shape
     top = chosen.shape[1]
     _need(chosen.shape == (tokens, top) and weights.shape == (tokens, top), "chosen and weights must be [tokens, top]")
-    _need(w_up.shape == (experts * ff, hidden) and w_down.shape == (experts * hidden, ff),
+    _need(w_up.shape == (experts * ff * (2 if gated else 1), hidden) and w_down.shape == (experts * hidden, ff),
           "the experts' stacked weights do not fit")
     act = torch.empty((tokens * top, ff), dtype=torch.float32, device=h.device)
     y = torch.empty((tokens, hidden), dtype=torch.float32, device=h.device)
     _call("mxb_experts_routed", h.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), chosen.data_ptr(),
-          weights.data_ptr(), act.data_ptr(), y.data_ptr(), tokens, hidden, experts, ff, top, _CODES[dtype], _stream())
+          weights.data_ptr(), act.data_ptr(), y.data_ptr(), tokens, hidden, experts, ff, top, _CODES[dtype],
+          1 if gated else 0, _stream())
+    return y
+
+
+def add_gated_rows(y: torch.Tensor, x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """y[t] += sigmoid(gate[t]) * x[t] (y float32, in place): ``gate`` is float32, one
+    number per token (a column of a wider tensor will do)."""
+    _check(y, "y", (torch.float32,), 2)
+    _check(x, "x", tuple(_CODES), 2)
+    _need(x.shape == y.shape, "x and y differ in shape")
+    _need(gate.is_cuda and gate.dtype == torch.float32 and gate.dim() in (1, 2) and gate.shape[0] == y.shape[0]
+          and (gate.dim() == 1 or gate.shape[1] == 1), "gate must be float32 [tokens] or [tokens, 1]")
+    _call("mxb_add_gated_rows", y.data_ptr(), x.data_ptr(), gate.data_ptr(), gate.stride(0), y.shape[0], y.shape[1],
+          _CODES[x.dtype], _stream())
     return y
 
 
@@ -759,6 +848,56 @@ def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.T
     out = torch.empty((tokens, width), dtype=out_dtype, device=x.device)
     _call("mxb_head_norm_gate", x.data_ptr(), weight.data_ptr(), _ptr(gate), ldg, gate_code, out.data_ptr(),
           _CODES[out_dtype], tokens, heads, width // heads, float(eps), _stream())
+    return out
+
+
+# ------------------------------------------------------------ the delta rule
+def delta_rule_max_dim() -> int:
+    return int(_fn("mxb_delta_rule_max_dim")())
+
+
+def delta_rule(qkv: torch.Tensor, offsets, beta: torch.Tensor, step: torch.Tensor, step_bias: torch.Tensor,
+               rate: torch.Tensor, state: torch.Tensor, row_start: torch.Tensor, row_length: torch.Tensor,
+               request_slots: torch.Tensor, heads: int, groups: int, dim: int, vdim: int) -> torch.Tensor:
+    """The gated delta rule with a decay per head and key channel over a step's
+    tokens. ``qkv`` ``[tokens, columns]`` holds, from the column ``offsets``
+    (q, k, v) on, groups * dim queries and keys and heads * vdim values (after
+    their convolution and activation); head h reads group h // (heads / groups).
+    ``beta`` float32 ``[tokens, heads]`` (a view of a wider tensor will do) are
+    the pre-activations of the write strength, ``step`` float32
+    ``[tokens, heads * dim]`` those of the step size, to which ``step_bias``
+    ``[heads * dim]`` is added; ``rate`` ``[heads]`` is positive. Per head:
+    q and k become unit vectors (q times dim^-1/2), g = exp(-rate softplus(step
+    + bias)), S <- g S (by rows); u = sigmoid(beta) (v - S^T k); S <- S + k u^T;
+    o = S^T q. ``state`` float32 ``[slots, heads, dim, vdim]`` is advanced in
+    place; request row r brings ``row_length[r]`` tokens from packed token
+    ``row_start[r]`` on (0: a padding row) and owns slot ``request_slots[r]``.
+    Returns float32 ``[tokens, heads * vdim]``."""
+    _need(qkv.is_cuda and qkv.dtype in _CODES and qkv.dim() == 2 and qkv.stride(1) == 1,
+          "qkv must be a CUDA [tokens, columns] tensor with unit column stride")
+    tokens = qkv.shape[0]
+    _need(beta.is_cuda and beta.dtype == torch.float32 and beta.dim() == 2 and beta.stride(1) == 1
+          and beta.shape == (tokens, heads), "beta must be float32 [tokens, heads]")
+    _need(step.is_cuda and step.dtype == torch.float32 and step.dim() == 2 and step.stride(1) == 1
+          and step.shape == (tokens, heads * dim), "step must be float32 [tokens, heads * dim]")
+    _check(step_bias, "step_bias", (torch.float32,), 1)
+    _check(rate, "rate", (torch.float32,), 1)
+    _need(step_bias.numel() == heads * dim and rate.numel() == heads, "step_bias or rate has the wrong size")
+    _check(state, "state", (torch.float32,), 4)
+    _need(state.shape[1:] == (heads, dim, vdim), f"state must be [slots, {heads}, {dim}, {vdim}]")
+    _need(heads % groups == 0 and 0 < dim <= delta_rule_max_dim(), "the head layout does not fit")
+    for name, tensor in (("row_start", row_start), ("row_length", row_length), ("request_slots", request_slots)):
+        _check(tensor, name, (torch.int32,), 1)
+    rows = row_start.numel()
+    _need(row_length.numel() == rows and request_slots.numel() >= rows, "row lists differ in length")
+    q_off, k_off, v_off = (int(o) for o in offsets)
+    _need(max(q_off + groups * dim, k_off + groups * dim, v_off + heads * vdim) <= qkv.shape[1],
+          "the column offsets reach beyond qkv")
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=qkv.device)
+    _call("mxb_delta_rule", qkv.data_ptr(), qkv.stride(0), q_off, k_off, v_off, beta.data_ptr(), beta.stride(0), 0,
+          step.data_ptr(), step.stride(0), step_bias.data_ptr(), rate.data_ptr(), state.data_ptr(), state.stride(0),
+          state.shape[0], row_start.data_ptr(), row_length.data_ptr(), request_slots.data_ptr(), out.data_ptr(), rows,
+          heads, groups, dim, vdim, _CODES[qkv.dtype], status_word(qkv.device).data_ptr(), _stream())
     return out
 
 
@@ -961,12 +1100,25 @@ def write_cache(k: torch.Tensor, v: torch.Tensor, cache: torch.Tensor, slots: to
 
 
 # ------------------------------------------------------------------ attention
+def _sink(sink, heads: int):
+    """(has_sink, score, pointer) as the attention kernels take a sink: None for
+    none, a number for one score that all heads share, or a float32 tensor
+    ``[heads]`` with a score per query head."""
+    if sink is None:
+        return 0, 0.0, None
+    if isinstance(sink, torch.Tensor):
+        _need(sink.is_cuda and sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == heads,
+              f"a sink per head must be {heads} contiguous float32 values on the device")
+        return 1, 0.0, sink.data_ptr()
+    return 1, float(sink), None
+
+
 def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor,
                          block_tables: torch.Tensor, tile_request: torch.Tensor,
                          tile_start: torch.Tensor, tile_length: torch.Tensor,
                          positions: torch.Tensor, scale: float, window: int = 0, chunk: int = 0,
                          gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                         gate_per_head: bool = False, sink: Optional[float] = None) -> torch.Tensor:
+                         gate_per_head: bool = False, sink=None) -> torch.Tensor:
     """Attention of every query token over its request's cached keys (itself
     included) in float32; q is [tokens, heads, head_dim], out
     [tokens, heads, value_dim] with value_dim at most head_dim (the first
@@ -1011,7 +1163,7 @@ def paged_attention_tile(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
           tile_start.data_ptr(), tile_length.data_ptr(), positions.data_ptr(), tiles, heads,
           kv_heads, head_dim, page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[dtype],
           _ptr(gate), gate_stride, planes, value_dim, float(softcap), 1 if gate_per_head else 0,
-          0 if sink is None else 1, float(sink or 0.0), status_word(q.device).data_ptr(), _stream())
+          *_sink(sink, heads), status_word(q.device).data_ptr(), _stream())
     return out
 
 
@@ -1060,7 +1212,7 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
                   tile_request: torch.Tensor, tile_start: torch.Tensor, tile_length: torch.Tensor,
                   positions: torch.Tensor, scale: float, window: int = 0, kernel: str = "auto",
                   longest_context: int = 0, chunk: int = 0, gate: Optional[torch.Tensor] = None,
-                  softcap: float = 0.0, sink: Optional[float] = None) -> torch.Tensor:
+                  softcap: float = 0.0, sink=None) -> torch.Tensor:
     """Causal attention of prompt portions on the tensor cores (bfloat16,
     float32 softmax and accumulation); tiles hold up to 128 consecutive tokens
     of one request. ``kernel``: "tcgen05" (TMA, tensor memory), "mma" (the
@@ -1106,7 +1258,7 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
               block_tables.data_ptr(), block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(),
               tile_length.data_ptr(), positions.data_ptr(), tokens, tiles, heads, kv_heads, head_dim,
               page_tokens, num_pages, int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], shares, _ptr(partial),
-              _ptr(gate), gate_stride, float(softcap), 0 if sink is None else 1, float(sink or 0.0),
+              _ptr(gate), gate_stride, float(softcap), *_sink(sink, heads),
               status_word(q.device).data_ptr(), _stream())
         if shares > 1:
             global _launches
@@ -1116,7 +1268,7 @@ def flash_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block
           block_tables.shape[1], tile_request.data_ptr(), tile_start.data_ptr(), tile_length.data_ptr(),
           positions.data_ptr(), tiles, heads, kv_heads, head_dim, page_tokens, num_pages,
           int(window or 0), int(chunk or 0), float(scale), _CODES[q.dtype], _ptr(gate), gate_stride, float(softcap),
-          0 if sink is None else 1, float(sink or 0.0), status_word(q.device).data_ptr(), _stream())
+          *_sink(sink, heads), status_word(q.device).data_ptr(), _stream())
     return out
 
 
@@ -1148,7 +1300,7 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
                            longest_context: int, window: int = 0,
                            partial: Optional[torch.Tensor] = None, chunk: int = 0,
                            gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                           sink: Optional[float] = None) -> torch.Tensor:
+                           sink=None) -> torch.Tensor:
     """Attention of single tokens over their requests' cached keys, split
     along the keys. ``row_token[i]`` is the token (row of q and out) of the
     i-th decoded request, negative for a padding row; ``row_request[i]`` its
@@ -1187,7 +1339,7 @@ def paged_attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tens
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
           int(window or 0), int(chunk or 0), float(scale), _CODES[dtype], _ptr(gate), gate_stride, float(softcap),
-          0 if sink is None else 1, float(sink or 0.0), status_word(q.device).data_ptr(), _stream())
+          *_sink(sink, heads), status_word(q.device).data_ptr(), _stream())
     return out
 
 
@@ -1216,7 +1368,7 @@ def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_t
                                    scale: float, longest_context: int, weight: torch.Tensor,
                                    window: int = 0, chunk: int = 0,
                                    gate: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                                   sink: Optional[float] = None) -> torch.Tensor:
+                                   sink=None) -> torch.Tensor:
     """``paged_attention_decode`` followed at once by the output projection
     ``weight`` ``[hidden, heads * head_dim]``, for steps of up to 64 tokens in
     bfloat16. Returns float32 ``[heads, tokens, hidden]``: the projection's sum
@@ -1244,7 +1396,7 @@ def paged_attention_decode_project(q: torch.Tensor, cache: torch.Tensor, block_t
           block_tables.data_ptr(), block_tables.shape[1], row_token.data_ptr(), row_request.data_ptr(),
           positions.data_ptr(), rows, tokens, heads, kv_heads, head_dim, page_tokens, num_pages, splits,
           int(window or 0), int(chunk or 0), float(scale), weight.data_ptr(), weight.stride(0), hidden, summands.data_ptr(),
-          _ptr(gate), gate_stride, float(softcap), 0 if sink is None else 1, float(sink or 0.0),
+          _ptr(gate), gate_stride, float(softcap), *_sink(sink, heads),
           status_word(q.device).data_ptr(), _stream())
     return summands
 
@@ -1318,11 +1470,15 @@ def gemm_skinny_takes(a: torch.Tensor, w: torch.Tensor, swiglu: bool = False) ->
     return gemm_stream_supported(a, w, swiglu) or gemm_skinny_supported(a, w)
 
 
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}   # act of a gated feed-forward, act(gate) * up
+
+
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                swiglu: bool = False, out: Optional[torch.Tensor] = None, kernel: str = "auto") -> torch.Tensor:
+                swiglu: bool = False, out: Optional[torch.Tensor] = None, kernel: str = "auto",
+                activation: str = "silu") -> torch.Tensor:
     """a [m <= 64, k] times w [n, k] transposed, reading w once. With
     ``swiglu`` w holds gate rows then up rows and the result is
-    silu(gate) * up, [m, n / 2]. ``kernel``: "stream" (rows of w by bulk copy
+    act(gate) * up, [m, n / 2], act being ``activation`` ("silu", "gelu_tanh"). ``kernel``: "stream" (rows of w by bulk copy
     into shared memory, m <= 16), "load" (16-byte loads into registers) or
     "auto": stream where it takes the shape, the output is not wider than
     STREAM_COLUMNS and k is at most STREAM_K (the layers of a small model,
@@ -1346,11 +1502,11 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch
     loads = gemm_skinny_supported(a, w)
     if streams and (kernel == "stream" or not loads or (columns <= STREAM_COLUMNS and k <= STREAM_K)):
         _call("mxb_gemm_stream", out.data_ptr(), _CODES[out_dtype], a.data_ptr(), w.data_ptr(), m, n, k,
-              a.stride(0), w.stride(0), out.stride(0), columns if swiglu else 0,
+              a.stride(0), w.stride(0), out.stride(0), columns if swiglu else 0, GATE_ACTIVATIONS[activation],
               status_word(a.device).data_ptr(), _stream())
         return out
     _call("mxb_gemm_skinny", out.data_ptr(), _CODES[out_dtype], a.data_ptr(), w.data_ptr(), m, n, k,
-          a.stride(0), w.stride(0), out.stride(0), columns if swiglu else 0, _stream())
+          a.stride(0), w.stride(0), out.stride(0), columns if swiglu else 0, GATE_ACTIVATIONS[activation], _stream())
     return out
 
 
@@ -1400,8 +1556,9 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.b
     return result
 
 
-def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i], float32 inside."""
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
+    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i], float32 inside; act is
+    silu, or with ``activation="gelu_tanh"`` the tanh form of gelu."""
     _check(gate_up, "gate_up", tuple(_CODES), 2)
     tokens, width = gate_up.shape
     _need(width % 2 == 0, "gate_up must hold gate and up side by side")
@@ -1411,7 +1568,7 @@ def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch
     _check(out, "out", (gate_up.dtype,), 2)
     _need(out.shape == (tokens, inter), "out has the wrong shape")
     _call("mxb_silu_mul", out.data_ptr(), gate_up.data_ptr(), _CODES[gate_up.dtype], tokens, inter,
-          _stream())
+          GATE_ACTIVATIONS[activation], _stream())
     return out
 
 

@@ -20,7 +20,13 @@ the wider of the two, the others padded with zeros). Values of another width
 than the keys run on the general kernel only; a per-head gate is spread over
 the head's values for the tensor-core kernels. ``sink`` adds one more key
 without a value to every query's softmax, with that score (0.0: the
-denominator is 1 + the sum). ``value_position`` (a rotary position part over
+denominator is 1 + the sum); a tensor's name instead of a number gives every
+query head a learned score of its own. ``q_bias`` / ``k_bias`` / ``v_bias``
+(tensor names) are added to the projections before their one rounding to the
+compute type. ``shared_kv`` marks a layer without key and value projections:
+it reads the rows another layer of the same head layout and rotation wrote
+into the cache entry it is given, with its own queries, mask, cap and sink.
+``value_position`` (a rotary position part over
 the values' width) turns the value of position j by j before it is cached and
 turns each head's output at position i back by i, so that what a query takes
 from a value depends on their distance.
@@ -218,23 +224,37 @@ class GQAttention:
         self.row_dim = max(self.head_dim, self.value_dim)      # width of a cached row
         # v_proj absent: the key projection's raw output is the values too. gate_proj: an
         # output gate over the concatenated heads, from the mixer's own input.
-        self.own_values = spec.get("v_proj") is not None
+        # shared_kv: no key or value projection at all; the cache entry another layer writes is read.
+        self.own_keys = not spec.get("shared_kv")
+        self.own_values = spec.get("v_proj") is not None and self.own_keys
         self.gated = spec.get("gate_proj") is not None
-        stacked = []
-        if not self.own_values and self.value_dim != self.head_dim:
+        stacked, biases, biased = [], [], False
+        if self.own_keys and not self.own_values and self.value_dim != self.head_dim:
             raise ValueError("values taken from the key projection are as wide as the keys")
         gate_rows = self.num_heads if self.gate_scope == "head" else self.out_size
-        for name, rows, present in (("q_proj", self.q_size, True), ("k_proj", self.kv_size, True),
-                                    ("v_proj", self.v_size, self.own_values),
-                                    ("gate_proj", gate_rows, self.gated)):
+        for name, rows, present, bias in (("q_proj", self.q_size, True, "q_bias"),
+                                          ("k_proj", self.kv_size, self.own_keys, "k_bias"),
+                                          ("v_proj", self.v_size, self.own_values, "v_bias"),
+                                          ("gate_proj", gate_rows, self.gated, None)):
             if not present:
                 continue
             weight = weights.take(spec[name])
             if tuple(weight.shape) != (rows, self.hidden_size):
                 raise ValueError(f"{spec[name]} is {tuple(weight.shape)}, expected {(rows, self.hidden_size)}")
             stacked.append(weight)
+            if bias is not None and spec.get(bias):
+                values = weights.take(spec[bias])
+                if values.numel() != rows:
+                    raise ValueError(f"{spec[bias]} has {values.numel()} values, expected {rows}")
+                biases.append(values.to(device=runtime.device, dtype=torch.float32).reshape(-1))
+                biased = True
+            else:
+                biases.append(torch.zeros(rows, dtype=torch.float32, device=runtime.device))
         # rows: all q heads, then k heads, then v heads (if any), then the gate (if any)
         self.qkv = Linear.stacked(stacked, runtime)
+        self.bias = torch.cat(biases).contiguous() if biased else None   # one value per row of the stacked product
+        if not self.own_keys:
+            self.kv_size = self.v_size = 0     # nothing of them in the stacked product
         self.gate_offset = self.q_size + self.kv_size + (self.v_size if self.own_values else 0)
         self.gate_rows = gate_rows
         self.o = Linear(weights.take(spec["o_proj"]), runtime)
@@ -243,7 +263,14 @@ class GQAttention:
         self.q_norm = build_part("norm", spec.get("q_norm"), weights, runtime)
         self.k_norm = build_part("norm", spec.get("k_norm"), weights, runtime)
         self.position = build_part("position", spec.get("position"), weights, runtime)
-        self.sink = None if spec.get("sink") is None else float(spec["sink"])
+        sink = spec.get("sink")
+        if isinstance(sink, str):     # a learned score per query head
+            values = weights.take(sink)
+            if values.numel() != self.num_heads:
+                raise ValueError(f"{sink} has {values.numel()} values, expected one per head ({self.num_heads})")
+            self.sink = values.to(device=runtime.device, dtype=torch.float32).reshape(-1).contiguous()
+        else:
+            self.sink = None if sink is None else float(sink)
         self.value_position = build_part("position", spec.get("value_position"), weights, runtime)
         if self.value_position is not None:
             if not getattr(self.value_position, "fused_tables", False) or self.value_position.head_dim != self.value_dim:
@@ -295,19 +322,31 @@ class GQAttention:
 
     def _attend(self, x: torch.Tensor, ctx: StepContext, cache: CacheView, summands: bool) -> torch.Tensor:
         tokens = x.shape[0]
-        qkv = self.qkv.forward(x)
+        if self.bias is not None:
+            # the product leaves in float32 and meets the bias there: one rounding to the compute type
+            qkv = ops.add_bias(self.qkv.forward(x, out_dtype=torch.float32), self.bias, self.dtype)
+        else:
+            qkv = self.qkv.forward(x)
         q = qkv[:, :self.q_size]
         k = qkv[:, self.q_size:self.q_size + self.kv_size]
         v = qkv[:, self.q_size + self.kv_size:self.q_size + self.kv_size + self.v_size] if self.own_values else k
         gate = qkv[:, self.gate_offset:self.gate_offset + self.gate_rows] if self.gated else None
         per_head = self.norm_scope == "head"
-        if self.value_position is not None:     # cached turned by their own position
+        if self.value_position is not None and self.own_keys:     # cached turned by their own position
             v = self._turn_values(v, ctx).view(tokens, self.v_size)
         if self.value_dim != self.head_dim:
             return self._attend_unequal(x, q, k, v, gate, ctx, cache)
         q_heads = torch.empty((tokens, self.num_heads, self.head_dim), dtype=self.dtype, device=x.device)
-        write = cache.write and cache.slots is not None
-        if self.fused:
+        write = cache.write and cache.slots is not None and self.own_keys
+        if not self.own_keys and self.fused:
+            # queries only: their norm and rotation; the keys and values are another layer's, in the cache already
+            q_heads = ops.norm_rotate_heads(
+                q, self.head_dim, ctx.positions, weight=self.q_norm.weight if self.q_norm is not None else None,
+                cos=self.position.cos if self.position is not None else None,
+                sin=self.position.sin if self.position is not None else None,
+                eps=self.q_norm.eps if self.q_norm is not None else 0.0,
+                interleaved=bool(getattr(self.position, "interleaved", False)), norm_scope=self.norm_scope)
+        elif self.fused:
             eps = self.q_norm.eps if self.q_norm is not None else (self.k_norm.eps if self.k_norm else 0.0)
             ops.qk_norm_rope_cache(
                 q, k, v, q_heads, cache.pool if write else None, cache.slots if write else None,
@@ -318,6 +357,9 @@ class GQAttention:
                 self.position.sin if self.position is not None else None, eps,
                 interleaved=bool(getattr(self.position, "interleaved", False)), norm_scope=self.norm_scope)
         else:
+            if not self.own_keys:
+                raise ValueError("a layer that reads another layer's keys needs head norms and a position part "
+                                 "that the fused kernel takes")
             if not self.own_values:
                 v = k   # as projected: before the norm and the rotation below
             if self.q_norm is not None:
@@ -358,6 +400,9 @@ class GQAttention:
         per_head = self.norm_scope == "head"
         parts = []
         for rows, norm, heads in ((q, self.q_norm, self.num_heads), (k, self.k_norm, self.num_kv_heads)):
+            if rows is k and not self.own_keys:
+                parts.append(None)     # another layer's keys and values, in the cache already
+                continue
             weight = norm.weight if norm is not None else None
             if norm is not None and not isinstance(norm, RMSNorm):
                 shape = (tokens * heads, self.head_dim) if per_head else (tokens, heads * self.head_dim)
@@ -373,7 +418,7 @@ class GQAttention:
         q_heads, k_heads = parts
         pad = lambda t, have: torch.nn.functional.pad(t, (0, width - have)) if have < width else t
         q_rows = pad(q_heads, self.head_dim).contiguous()
-        if cache.write and cache.slots is not None:
+        if cache.write and cache.slots is not None and self.own_keys:
             k_rows = pad(k_heads, self.head_dim).reshape(tokens, self.num_kv_heads * width)
             v_rows = pad(v.reshape(tokens, self.num_kv_heads, self.value_dim), self.value_dim) \
                 .reshape(tokens, self.num_kv_heads * width)

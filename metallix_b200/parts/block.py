@@ -25,6 +25,13 @@ optional: what a sublayer reads passes a short causal convolution over time
 first (h <- h + conv(h), whose last inputs are part of a request's state),
 and after the feed-forward the layer takes an input from the token itself,
 x <- x + norm(input(x, token)).
+
+``parallel_residual`` lets both sublayers read the same input:
+x' = x + m (mixer(norm1(x)) + feed_forward(norm2(x))) with a constant m, the
+feed-forward being optional. What the layer leaves is a ``PairSum`` (the two
+results and m); the next layer's first kernel adds it to the stream and makes
+both of that layer's norms from one pass over the row (two RMS norms of the
+same row share its mean square).
 """
 from __future__ import annotations
 
@@ -282,3 +289,66 @@ class ConvPreNormBlock:
 
 register_part("block", "conv_prenorm_residual",
               lambda layer, weights, runtime: ConvPreNormBlock(layer, weights, runtime))
+
+
+@dataclass
+class PairSum:
+    """Two sublayers' results on their way into the residual stream: x += scale * (first + second)."""
+
+    first: torch.Tensor
+    second: Optional[torch.Tensor]
+    scale: float
+
+    def settle(self, residual: torch.Tensor) -> None:
+        ops.pair_add_rmsnorm(residual, self.first, self.second, self.scale, None, None, 0.0, torch.float32)
+
+
+class ParallelResidualBlock:
+    """x <- x + m (mixer(norm1(x)) + feed_forward(norm2(x))): both sublayers on the same x."""
+
+    kind = "parallel_residual"
+
+    def __init__(self, layer: LayerSpec, weights: WeightStore, runtime: Runtime):
+        from .norm import RMSNorm
+        self.name = layer.name
+        self.scale = float(layer.block.get("residual_scale", 1.0))
+        self.mixer_norm = build_part("norm", layer.mixer_norm, weights, runtime)
+        self.mixer = build_part("mixer", layer.mixer, weights, runtime)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward, weights, runtime)
+        self.feed_forward_norm = None
+        if self.feed_forward is not None:
+            if layer.feed_forward_norm is None:
+                raise ValueError(f"{layer.name}: a feed-forward needs its norm")
+            self.feed_forward_norm = build_part("norm", layer.feed_forward_norm, weights, runtime)
+        self.dtype = runtime.dtype
+        norms = [n for n in (self.mixer_norm, self.feed_forward_norm) if n is not None]
+        vector = 8 if self.dtype == torch.bfloat16 else 4
+        # one kernel for the sum and both norms: RMS norms with one epsilon over rows the kernel's vectors divide
+        self.fused = (all(isinstance(n, RMSNorm) for n in norms) and len({n.eps for n in norms}) == 1
+                      and layer.block["hidden_size"] % vector == 0)
+
+    def parts(self):
+        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+
+    def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: CacheView):
+        first = second = None
+        scale = 1.0
+        if isinstance(pending, PairSum) and self.fused:
+            first, second, scale = pending.first, pending.second, pending.scale
+        elif pending is not None:
+            settle(residual, pending)
+        if self.fused:
+            second_weight = self.feed_forward_norm.weight if self.feed_forward_norm is not None else None
+            normed = ops.pair_add_rmsnorm(residual, first, second, scale, self.mixer_norm.weight, second_weight,
+                                          self.mixer_norm.eps, self.dtype)
+            mixer_in, feed_in = normed if second_weight is not None else (normed, None)
+        else:
+            mixer_in = self.mixer_norm.forward(residual, self.dtype)
+            feed_in = self.feed_forward_norm.forward(residual, self.dtype) if self.feed_forward is not None else None
+        mixed = self.mixer.forward(mixer_in, ctx, cache)
+        fed = self.feed_forward.forward(feed_in, ctx) if self.feed_forward is not None else None
+        return PairSum(mixed, fed, self.scale)
+
+
+register_part("block", "parallel_residual",
+              lambda layer, weights, runtime: ParallelResidualBlock(layer, weights, runtime))

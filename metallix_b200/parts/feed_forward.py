@@ -1,7 +1,8 @@
 """SwiGLU feed-forward: d = ((sigmoid(g) * g) * u) Wd^T with g = m Wg^T and
 u = m Wu^T (crates/models/qwen/src/forward.rs:1904-1920). Gate and up weights
 are stacked so that one product yields both; SiLU and the product with u are
-float32 inside the kernel.
+float32 inside the kernel. ``activation="gelu_tanh"`` puts the tanh form of
+gelu in SiLU's place, in every kernel that holds the activation.
 
 ``dense_ff`` is the feed-forward without a gate: d = act(m Wu^T) Wd^T, the
 activation a parameter (``relu_squared``: max(z, 0)^2).
@@ -10,7 +11,12 @@ activation a parameter (``relu_squared``: max(z, 0)^2).
 of ``experts`` (+ ``identity`` outputs that stand for experts returning their
 input) per token by softmax score plus a correction, and the output is the sum
 of the chosen experts' outputs weighted by their scores over the chosen
-scores' sum."""
+scores' sum. Parameters widen it: ``scores="sigmoid"`` scores every output on
+its own; ``groups`` = (count, keep) lets the choice fall only on the best
+groups of neighbouring experts; ``scale`` multiplies the weights;
+``activation="swiglu"`` makes an expert a gated feed-forward
+down(silu(gate(h)) * up(h)); ``shared`` names a gated feed-forward that every
+token uses, added behind a sigmoid gate of one number per token."""
 from __future__ import annotations
 
 import torch
@@ -18,7 +24,7 @@ import torch
 from .. import ops
 from ..config.spec import PartSpec
 from .linear import Linear
-from .registry import Runtime, StepContext, WeightStore, register_part
+from .registry import Runtime, StepContext, WeightStore, build_part, register_part
 
 FUSED_ACTIVATION_ROWS = 1536   # from here on "auto" takes the tcgen05 product with the SwiGLU epilogue
 
@@ -37,13 +43,16 @@ class SwiGLU:
         self.gate_up = Linear.stacked([gate, up], runtime)  # rows: gate, then up
         self.down = Linear(down, runtime)
         self.intermediate_size = inter
+        self.activation = spec.get("activation") or "silu"
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r}; one of {sorted(ops.GATE_ACTIVATIONS)}")
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         few = ops.SKINNY_ROWS if x.shape[1] <= ops.STREAM_K else ops.SKINNY_ROWS // 2   # as ops.gemm_bf16
         if (x.shape[0] <= few and self.gate_up.backend in ("auto", "skinny")
                 and ops.gemm_skinny_takes(x, self.gate_up.weight, swiglu=True)):
             # A decode step: gate, up and the activation in one pass over the weights.
-            return self.down.forward(ops.gemm_skinny(x, self.gate_up.weight, swiglu=True))
+            return self.down.forward(ops.gemm_skinny(x, self.gate_up.weight, swiglu=True, activation=self.activation))
         # From about 1,500 rows on the tcgen05 product with the activation in its
         # epilogue beats the library's product followed by an activation pass
         # (28 against 31 us at 2,048 rows of this model; 21 against 19 at 1,024,
@@ -55,8 +64,8 @@ class SwiGLU:
             from .. import tensor_core
             if tensor_core.supports(x, self.gate_up.weight, torch.bfloat16):
                 # gate, up and the activation in the product's epilogue
-                return self.down.forward(tensor_core.gemm_swiglu(x, self.gate_up.weight))
-        return self.down.forward(ops.silu_mul(self.gate_up.forward(x)))
+                return self.down.forward(tensor_core.gemm_swiglu(x, self.gate_up.weight, activation=self.activation))
+        return self.down.forward(ops.silu_mul(self.gate_up.forward(x), activation=self.activation))
 
     def weight_bytes(self) -> int:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
@@ -103,7 +112,7 @@ class RoutedExperts:
 
     kind = "routed_experts"
     ROUTED_TOKENS = 1     # from two tokens on experts are shared often enough for the grouped products to read less
-    ACTIVATIONS = ("relu_squared",)
+    ACTIVATIONS = ("relu_squared", "swiglu")
 
     def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
         hidden, ff = spec["hidden_size"], spec["intermediate_size"]
@@ -113,20 +122,45 @@ class RoutedExperts:
             raise ValueError(f"top {self.top} of {outputs} router outputs (at most {ops.ROUTER_OUTPUTS}) cannot be chosen")
         if spec["activation"] not in self.ACTIVATIONS:
             raise ValueError(f"activation {spec['activation']!r}; one of {self.ACTIVATIONS}")
+        self.gated = spec["activation"] == "swiglu"
+        self.scores = spec.get("scores") or "softmax"
+        self.groups = tuple(int(v) for v in spec["groups"]) if spec.get("groups") else None
+        self.weight_scale = float(spec.get("scale") or 1.0)
+        if self.scores not in ("softmax", "sigmoid"):
+            raise ValueError(f"scores {self.scores!r}; 'softmax' or 'sigmoid'")
+        if self.groups is not None:
+            count, keep = self.groups
+            if count < 1 or outputs % count or not 1 <= keep <= count or keep * (outputs // count) < self.top:
+                raise ValueError(f"{count} groups of which {keep} are kept do not fit {outputs} outputs and top {self.top}")
         ups, downs = [], []
         for index in range(self.experts):
             up, down = weights.take(spec["up_proj"].format(index)), weights.take(spec["down_proj"].format(index))
             if tuple(up.shape) != (ff, hidden) or tuple(down.shape) != (hidden, ff):
                 raise ValueError(f"expert {index}: up is {tuple(up.shape)}, down is {tuple(down.shape)}; "
                                  f"expected {(ff, hidden)} and {(hidden, ff)}")
+            if self.gated:   # an expert's gate rows, then its up rows
+                gate = weights.take(spec["gate_proj"].format(index))
+                if tuple(gate.shape) != (ff, hidden):
+                    raise ValueError(f"expert {index}: gate is {tuple(gate.shape)}, expected {(ff, hidden)}")
+                ups.append(gate.to(runtime.device))
             ups.append(up.to(runtime.device))
             downs.append(down.to(runtime.device))
-        # up: rows e * ff + f; down: rows e * hidden + c: one expert's matrix after the other
+        # up: rows e * ff + f (gated: e * 2 ff + f for the gate, + ff for up); down: rows e * hidden + c:
+        # one expert's matrix after the other
         self.up = Linear(torch.cat(ups, dim=0), runtime) if ups else None
         self.down = Linear(torch.cat(downs, dim=0), runtime) if downs else None
         router = weights.take(spec["router"])
         if tuple(router.shape) != (outputs, hidden):
             raise ValueError(f"{spec['router']} is {tuple(router.shape)}, expected {(outputs, hidden)}")
+        self.outputs = outputs
+        self.shared = None
+        if spec.get("shared") is not None:
+            # an expert for every token, out += sigmoid(h . w) shared(h): its gate's row rides under the router's
+            self.shared = build_part("feed_forward", spec["shared"], weights, runtime)
+            gate = weights.take(spec["shared_gate"])
+            if gate.numel() != hidden:
+                raise ValueError(f"{spec['shared_gate']} has {gate.numel()} values, expected {hidden}")
+            router = torch.cat([router.to(runtime.device), gate.reshape(1, hidden).to(runtime.device)], dim=0)
         self.router = Linear(router, runtime)
         correction = weights.take(spec["correction"]) if spec.get("correction") else torch.zeros(outputs)
         if correction.numel() != outputs:
@@ -137,18 +171,26 @@ class RoutedExperts:
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         """float32 ``[tokens, hidden]``."""
         logits = self.router.forward(x, out_dtype=torch.float32)
-        chosen, weights, dense, on_identity = ops.route_experts(logits, self.correction, self.experts, self.top)
+        out = self._routed(x, logits[:, :self.outputs])
+        if self.shared is not None:
+            ops.add_gated_rows(out, self.shared.forward(x, ctx), logits[:, self.outputs:])
+        return out
+
+    def _routed(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        chosen, weights, dense, on_identity = ops.route_experts(logits, self.correction, self.experts, self.top,
+                                                                scores=self.scores, groups=self.groups,
+                                                                scale=self.weight_scale)
         if self.up is None:     # identity experts only
             return ops.experts_add_identity(torch.zeros(x.shape, dtype=torch.float32, device=x.device), x, on_identity)
         if x.shape[0] > self.ROUTED_TOKENS and self.grouped(x):
             from .. import tensor_core
             position, tile_group, rows = ops.expert_rows(chosen, self.experts)
             act = tensor_core.gemm_grouped(ops.expert_gather_rows(x, position, rows), self.up.weight, tile_group,
-                                           self.experts, tensor_core.RELU_SQUARED)
+                                           self.experts, tensor_core.SWIGLU if self.gated else tensor_core.RELU_SQUARED)
             out = tensor_core.gemm_grouped(act, self.down.weight, tile_group, self.experts, tensor_core.STORE_F32)
             return ops.expert_combine_rows(out, position, weights, on_identity, x)
         return ops.experts_routed(x, self.up.weight, self.down.weight, chosen, weights, self.experts,
-                                  self.intermediate_size)
+                                  self.intermediate_size, gated=self.gated)
 
     def grouped(self, x: torch.Tensor) -> bool:
         """Whether the grouped tensor-core products take this step."""
@@ -159,7 +201,8 @@ class RoutedExperts:
     def weight_bytes(self) -> int:
         """What a decode step of one token reads: the router and ``top`` experts."""
         per_expert = (self.up.weight_bytes() + self.down.weight_bytes()) // self.experts if self.up is not None else 0
-        return self.router.weight_bytes() + min(self.top, self.experts) * per_expert
+        shared = self.shared.weight_bytes() if self.shared is not None else 0
+        return self.router.weight_bytes() + min(self.top, self.experts) * per_expert + shared
 
 
 register_part("feed_forward", "routed_experts", lambda spec, weights, runtime: RoutedExperts(spec, weights, runtime))

@@ -18,6 +18,12 @@ attention with H query heads over one shared key/value head, whatever the
 context's length. That is ``cache_mode="latent"``: the least memory, on the
 general attention kernel.
 
+Without ``q_rank`` the queries come from one projection, q = a Wq^T, with no
+latent of their own. ``window`` lets a query see only the last that many
+positions (its own included), ``sink`` adds one more key without a value to
+every query's softmax, with one score for all heads (a number) or a learned
+score per head (a tensor's name); both reach whichever kernel serves the step.
+
 ``cache_mode="heads"`` keeps the equations in their first order instead: every
 position's latent is widened once, when it arrives, to each head's key
 [k_h | rot(kr)] and value v_h, and those rows are cached per head (padded
@@ -46,7 +52,7 @@ class LatentAttention:
     def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
         hidden = spec["hidden_size"]
         self.heads, self.dim, self.rot = spec["num_heads"], spec["head_dim"], spec["rotary_head_dim"]
-        self.vdim, self.rank, self.q_rank = spec["value_dim"], spec["kv_rank"], spec["q_rank"]
+        self.vdim, self.rank, self.q_rank = spec["value_dim"], spec["kv_rank"], spec.get("q_rank") or 0
         self.scale, self.eps = float(spec["scale"]), float(spec["eps"])
         self.width = self.rank + self.rot           # what a position's cache row holds
         if not 0 < self.width <= 576:
@@ -59,10 +65,23 @@ class LatentAttention:
                 raise ValueError(f"{spec[name]} is {tuple(weight.shape)}, expected {shape}")
             return weight
 
-        self.dq = Linear(matrix("q_down_proj", (self.q_rank, hidden)), runtime)
-        self.uq = Linear(matrix("q_up_proj", (H * (D + R), self.q_rank)), runtime)
+        if self.q_rank:
+            self.dq = Linear(matrix("q_down_proj", (self.q_rank, hidden)), runtime)
+            self.uq = Linear(matrix("q_up_proj", (H * (D + R), self.q_rank)), runtime)
+            self.q_norm = build_part("norm", spec["q_norm"], weights, runtime)
+        else:   # queries straight from the mixer's input
+            self.dq, self.q_norm = None, None
+            self.uq = Linear(matrix("q_proj", (H * (D + R), hidden)), runtime)
         self.dkv = Linear(matrix("kv_down_proj", (self.width, hidden)), runtime)
-        self.q_norm = build_part("norm", spec["q_norm"], weights, runtime)
+        self.window = int(spec.get("window") or 0)
+        sink = spec.get("sink")
+        if isinstance(sink, str):
+            values = weights.take(sink)
+            if values.numel() != H:
+                raise ValueError(f"{sink} has {values.numel()} values, expected one per head ({H})")
+            self.sink = values.to(device=runtime.device, dtype=torch.float32).reshape(-1).contiguous()
+        else:
+            self.sink = None if sink is None else float(sink)
         self.kv_norm = build_part("norm", spec["kv_norm"], weights, runtime)
         on_device = lambda t: t.to(device=runtime.device, dtype=runtime.dtype).contiguous()
         uk = on_device(matrix("k_up_proj", (H * D, self.rank))).view(H, D, self.rank)
@@ -94,8 +113,14 @@ class LatentAttention:
 
     def cache_need(self) -> CacheNeed:
         if self.per_head:
-            return CacheNeed(kind="kv_pages", kv_heads=self.heads, head_dim=self.head_size)
-        return CacheNeed(kind="kv_pages", kv_heads=1, head_dim=self.width, planes=1)
+            return CacheNeed(kind="kv_pages", kv_heads=self.heads, head_dim=self.head_size, window=self.window or None)
+        return CacheNeed(kind="kv_pages", kv_heads=1, head_dim=self.width, planes=1, window=self.window or None)
+
+    def _queries(self, x: torch.Tensor) -> torch.Tensor:
+        """[tokens, H * (D + R)]: through their own normed latent, or straight from the input."""
+        if self.dq is None:
+            return self.uq.forward(x)
+        return self.uq.forward(self.q_norm.forward(self.dq.forward(x), self.dtype))
 
     def parts(self):
         return [self.q_norm, self.kv_norm, self.position]
@@ -112,7 +137,7 @@ class LatentAttention:
             ops.latent_cache(self.dkv.forward(x), self.kv_norm.weight, self.kv_norm.eps, r, cache.pool, cache.slots,
                              ctx.positions, cos, sin, paired)
         # queries: through their own latent, then onto the cache's side
-        q = self.uq.forward(self.q_norm.forward(self.dq.forward(x), self.dtype))       # [tokens, H * (D + R)]
+        q = self._queries(x)                                                            # [tokens, H * (D + R)]
         q_heads = q.view(tokens, H, D + R)
         q_cache = torch.empty((tokens, H, self.width), dtype=self.dtype, device=x.device)
         if self.dtype == torch.float32:
@@ -124,7 +149,8 @@ class LatentAttention:
         tiles = tiles_of(ctx)
         mixed = torch.empty((tokens, H, r), dtype=self.dtype, device=x.device)
         ops.paged_attention_tile(q_cache, cache.pool, mixed, cache.block_tables, tiles["tile_request"],
-                                 tiles["tile_start"], tiles["tile_length"], ctx.positions, self.scale)
+                                 tiles["tile_start"], tiles["tile_length"], ctx.positions, self.scale, self.window,
+                                 sink=self.sink)
         # latents back to values, head by head
         if self.dtype == torch.float32:
             values = torch.empty((tokens, H * V), dtype=self.dtype, device=x.device)
@@ -140,20 +166,21 @@ class LatentAttention:
         rows = ops.latent_cache(self.dkv.forward(x), self.kv_norm.weight, self.kv_norm.eps, r, None, None,
                                 ctx.positions, cos, sin, paired)
         widened = self.kv_up.forward(rows[:, :r])                                       # [tokens, H * D + H * V]
-        q = self.uq.forward(self.q_norm.forward(self.dq.forward(x), self.dtype))       # [tokens, H * (D + R)]
+        q = self._queries(x)                                                            # [tokens, H * (D + R)]
         q_heads = torch.empty((tokens, H, hd), dtype=self.dtype, device=x.device)
         write = cache.write and cache.slots is not None
         ops.latent_heads(q, widened, rows, r, q_heads, cache.pool if write else None, cache.slots if write else None,
                          ctx.positions, cos, sin, paired, D, R, V)
-        out, _ = attend_cached(q_heads, cache, ctx, scale=self.scale, split_decode=self.split_decode, flash=self.flash)
+        out, _ = attend_cached(q_heads, cache, ctx, scale=self.scale, window=self.window, split_decode=self.split_decode,
+                               flash=self.flash, sink=self.sink)
         return self.o.forward(out.view(tokens, H * hd))
 
     def weight_bytes(self) -> int:
+        queries = self.uq.weight_bytes() + (self.dq.weight_bytes() if self.dq is not None else 0)
         if self.per_head:
-            return (self.dq.weight_bytes() + self.uq.weight_bytes() + self.dkv.weight_bytes() + self.o.weight_bytes()
-                    + self.kv_up.weight_bytes())
+            return queries + self.dkv.weight_bytes() + self.o.weight_bytes() + self.kv_up.weight_bytes()
         element = self.uk.element_size()
-        return (self.dq.weight_bytes() + self.uq.weight_bytes() + self.dkv.weight_bytes() + self.o.weight_bytes()
+        return (queries + self.dkv.weight_bytes() + self.o.weight_bytes()
                 + (self.uk.numel() + self.uv.numel()) * element)
 
 

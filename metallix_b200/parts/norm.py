@@ -38,6 +38,9 @@ class RMSNorm:
         ``delta`` may be float32 ``[parts, rows, size]``: its parts are added up
         first. A ``Pending`` delta passes its own norm before the sum, in the
         same pass over the row when that norm is an RMSNorm too."""
+        if delta is not None and hasattr(delta, "settle"):   # a block arrangement's own way of joining the stream
+            delta.settle(residual)
+            delta = None
         if delta is None:
             return ops.rmsnorm(residual, self.weight, self.eps, out_dtype)
         if isinstance(delta, Pending):

@@ -14,6 +14,14 @@ than ``high`` times keeps its frequency; one that turns fewer than ``low``
 times gets f_i / factor; in between the two are mixed, f_i (s + (1 - s) /
 factor) with s = (n_i - low) / (high - low) rising from 0 to 1.
 
+A second form of ``scaling`` (keys factor, original, fast, slow: the one known
+as YaRN) places the ramp on the pair index instead. With
+where(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), the index of the
+pair that makes t turns over ``original`` positions, lo = max(floor(where(fast)),
+0), hi = min(ceil(where(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) /
+max(hi - lo, 0.001), 0, 1), pair i gets f_i / factor * ramp_i + f_i (1 - ramp_i),
+and cos and sin are both multiplied by 0.1 ln(factor) + 1 (``rotary_magnitude``).
+
 Angles are formed in float64 (position times frequency), cos and sin are
 rounded once to float32 tables that the kernels index by position.
 """
@@ -34,7 +42,17 @@ def rotary_frequencies(theta: float, rotary_dim: int, scaling: Optional[Mapping]
     ``scaling`` (factor, low, high, original) as described above."""
     index = torch.arange(rotary_dim // 2, dtype=torch.float64)
     frequency = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * index / rotary_dim)
-    if scaling:
+    if scaling and "fast" in scaling:
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+        fast, slow = float(scaling["fast"]), float(scaling["slow"])
+        if not (factor > 0.0 and original > 0.0 and fast > 0.0 and slow > 0.0 and float(theta) > 1.0):
+            raise ValueError(f"rotary scaling needs positive factor, original, fast and slow, got {dict(scaling)}")
+        where = lambda turns: rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+        lo = max(math.floor(where(fast)), 0)
+        hi = min(math.ceil(where(slow)), rotary_dim - 1)
+        ramp = torch.clamp((index - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        frequency = frequency / factor * ramp + frequency * (1.0 - ramp)
+    elif scaling:
         factor, low, high = float(scaling["factor"]), float(scaling["low"]), float(scaling["high"])
         original = float(scaling["original"])
         if not (factor > 0.0 and high > low and original > 0.0):
@@ -44,6 +62,14 @@ def rotary_frequencies(theta: float, rotary_dim: int, scaling: Optional[Mapping]
         mixed = frequency * (share + (1.0 - share) / factor)
         frequency = torch.where(turns > high, frequency, torch.where(turns < low, frequency / factor, mixed))
     return frequency
+
+
+def rotary_magnitude(scaling: Optional[Mapping] = None) -> float:
+    """What cos and sin are multiplied by: 0.1 ln(factor) + 1 for the form of
+    ``scaling`` with fast and slow, else 1."""
+    if scaling and "fast" in scaling:
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 def _scaling_key(scaling: Optional[Mapping]) -> tuple:
@@ -69,8 +95,9 @@ class Rotary:
             frequency = rotary_frequencies(self.theta, rotary_dim, self.scaling).to(runtime.device)
             position = torch.arange(runtime.max_positions, dtype=torch.float64, device=runtime.device)
             angle = position[:, None] * frequency[None, :]
-            runtime.shared[key] = (torch.cos(angle).to(torch.float32).contiguous(),
-                                   torch.sin(angle).to(torch.float32).contiguous())
+            magnitude = rotary_magnitude(self.scaling)
+            runtime.shared[key] = ((torch.cos(angle) * magnitude).to(torch.float32).contiguous(),
+                                   (torch.sin(angle) * magnitude).to(torch.float32).contiguous())
         self.cos, self.sin = runtime.shared[key]
         self._shared, self._key = runtime.shared, key
 

@@ -210,3 +210,110 @@ class SelectiveScan:
 
 
 register_part("mixer", "selective_scan", lambda spec, weights, runtime: SelectiveScan(spec, weights, runtime))
+
+
+class ChannelDelta:
+    """The gated delta rule with one decay per head and key channel. With H
+    heads over G groups of queries and keys (head h reads group h // (H / G)),
+    key width D and value width V:
+
+        [q | k | v] = conv(a [Wq; Wk; Wv]^T), then silu      a short causal convolution per channel
+        qn = q / sqrt(sum q^2 + 1e-6) * D^-1/2,  kn = k / sqrt(sum k^2 + 1e-6)       per head
+        beta = sigmoid(a Wb^T)                               one per head
+        g = exp(-exp(A_log_h) * softplus((a Wa1^T) Wa2^T + dt_bias))   [H, D], rows of S
+        S <- g S;  u = beta (v - S^T kn);  S <- S + kn u^T;  o = S^T qn                per head
+
+    Each head's o over its root mean square times a weight over V (shared by
+    the heads) times sigmoid((a Wg1^T) Wg2^T), then Wo. S (float32
+    ``[H, D, V]``) and the convolution's last inputs are kept per request in
+    the cache's state slots. One product gives q, k, v, the write strength and
+    both low-rank inputs in float32; unit norms, decay, beta, the recurrence
+    and the head norm are float32 in both precisions; the convolution and its
+    activation hand on the compute type."""
+
+    kind = "channel_delta"
+    graph_safe = True
+    step_key = "request_rows"
+    prepare_step = staticmethod(request_rows)
+
+    def __init__(self, spec: PartSpec, weights: WeightStore, runtime: Runtime):
+        from .short_conv import ShortConv
+        hidden = spec["hidden_size"]
+        self.heads, self.groups = int(spec["num_heads"]), int(spec.get("num_kv_heads") or spec["num_heads"])
+        self.dim, self.vdim, self.eps = int(spec["head_dim"]), int(spec["value_dim"]), float(spec["eps"])
+        if self.heads % self.groups:
+            raise ValueError(f"{self.heads} heads cannot share {self.groups} groups of queries and keys")
+        if not 0 < self.dim <= ops.delta_rule_max_dim():
+            raise ValueError(f"keys of {self.dim} channels; the recurrence takes up to {ops.delta_rule_max_dim()}")
+        H, G, D, V = self.heads, self.groups, self.dim, self.vdim
+
+        def matrix(name, shape):
+            weight = weights.take(spec[name])
+            if tuple(weight.shape) != shape:
+                raise ValueError(f"{spec[name]} is {tuple(weight.shape)}, expected {shape}")
+            return weight
+
+        def vector(name, size):
+            tensor = weights.take(spec[name])
+            if tensor.numel() != size:
+                raise ValueError(f"{spec[name]} has {tensor.numel()} values, expected {size}")
+            return tensor.to(device=runtime.device, dtype=torch.float32).reshape(-1).contiguous()
+
+        # the two low ranks are sizes that only the checkpoint's tensors give
+        step_rank, gate_rank = weights.shape(spec["step_down_proj"])[0], weights.shape(spec["gate_down_proj"])[0]
+        self.conv_channels = 2 * G * D + H * V
+        stacked, self.offsets, cursor = [], {}, 0
+        for name, rows in (("q_proj", G * D), ("k_proj", G * D), ("v_proj", H * V), ("beta_proj", H),
+                           ("step_down_proj", step_rank), ("gate_down_proj", gate_rank)):
+            stacked.append(matrix(name, (rows, hidden)))
+            self.offsets[name] = cursor
+            cursor += rows
+        self.inputs = Linear.stacked(stacked, runtime)     # rows: q, k, v, write strength, step latent, gate latent
+        self.step_rank, self.gate_rank = step_rank, gate_rank
+        self.step_up = Linear(matrix("step_up_proj", (H * D, step_rank)), runtime)
+        self.gate_up = Linear(matrix("gate_up_proj", (H * V, gate_rank)), runtime)
+        self.step_bias = vector("step_bias", H * D)
+        self.rate = torch.exp(vector("a_log", H)).contiguous()
+        self.norm_weight = vector("norm", V).repeat(H).contiguous()       # one weight over V, the same for every head
+        taps = int(spec["conv_taps"])
+        conv_weight = torch.cat([matrix(name, (rows, taps)) for name, rows in
+                                 (("q_conv", G * D), ("k_conv", G * D), ("v_conv", H * V))], dim=0)
+        store = WeightStore({"conv": conv_weight})
+        self.conv = ShortConv(PartSpec("short_conv", {"channels": self.conv_channels, "taps": taps, "weight": "conv",
+                                                      "bias": None, "activation": "silu"}), store, runtime)
+        self.o = Linear(matrix("o_proj", (hidden, H * V)), runtime)
+        self.dtype = runtime.dtype
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed(kind="several", members=(
+            CacheNeed(kind="state", state_shape=(self.heads, self.dim, self.vdim), state_dtype="float32"),
+            self.conv.cache_need()))
+
+    def parts(self):
+        return [self.conv]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        if len(cache.members) != 2 or cache.members[0].state is None:
+            raise ValueError("the delta-rule mixer needs its two state entries of the cache")
+        rows = request_rows_of(ctx)
+        H, G, D, V, at = self.heads, self.groups, self.dim, self.vdim, self.offsets
+        proj = self.inputs.forward(x, out_dtype=torch.float32)
+        qkv = proj[:, :self.conv_channels]
+        if self.dtype != torch.float32:
+            qkv = qkv.to(self.dtype)       # what the projections hand on
+        qkv = self.conv.forward(qkv, ctx, cache.members[1])
+        low = proj[:, at["step_down_proj"]:at["step_down_proj"] + self.step_rank].to(self.dtype).contiguous()
+        step = self.step_up.forward(low, out_dtype=torch.float32)
+        mixed = ops.delta_rule(qkv, (0, G * D, 2 * G * D), proj[:, at["beta_proj"]:at["beta_proj"] + H], step,
+                               self.step_bias, self.rate, cache.members[0].state, rows["row_start"],
+                               rows["row_length"], ctx.request_slots, H, G, D, V)
+        low = proj[:, at["gate_down_proj"]:at["gate_down_proj"] + self.gate_rank].to(self.dtype).contiguous()
+        gate = self.gate_up.forward(low, out_dtype=torch.float32)
+        return self.o.forward(ops.head_norm_gate(mixed, self.norm_weight, gate, H, self.eps, self.dtype))
+
+    def weight_bytes(self) -> int:
+        return (self.inputs.weight_bytes() + self.step_up.weight_bytes() + self.gate_up.weight_bytes()
+                + self.o.weight_bytes())
+
+
+register_part("mixer", "channel_delta", lambda spec, weights, runtime: ChannelDelta(spec, weights, runtime))

@@ -74,6 +74,12 @@ class WeightStore:
     def has(self, name: str) -> bool:
         return name in self._tensors
 
+    def shape(self, name: str) -> tuple:
+        """A tensor's shape without taking it: for a size that only the checkpoint gives."""
+        if name not in self._tensors:
+            raise KeyError(f"weight {name!r} is not in the checkpoint")
+        return tuple(self._tensors[name].shape)
+
     def drop_taken(self, keep=()) -> None:
         """Forgets the tensors that parts have taken (except ``keep``), for an
         owner that hands its dictionary over: a part that stacked or cast a

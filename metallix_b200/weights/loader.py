@@ -4,7 +4,8 @@ Discovery, naming and the required-tensor check follow the reference's
 ``Qwen3CheckpointInspection`` (``crates/models/qwen/src/checkpoint.rs:51-134``):
 every regular ``*.safetensors`` file of the folder in sorted order (``:235-269``),
 bare or ``model.``-prefixed names made canonical (``:193-233``), every required
-tensor present with the configured shape (``:772-875``). Unlike the reference,
+tensor present with the configured shape (``:772-875``; a configured size of
+None is one that only the tensor gives). Unlike the reference,
 which stops at the first problem, all problems of a folder are gathered into
 one error that lists missing tensors, unexpected tensors and wrong shapes.
 
@@ -54,6 +55,12 @@ def canonical_names(entries: Mapping[str, TensorEntry]) -> Dict[str, TensorEntry
     return out
 
 
+def _fits(found: tuple, expected: tuple) -> bool:
+    """Whether a stored shape is the configured one; None in the configured shape
+    stands for a size that config.json leaves to the tensor."""
+    return len(found) == len(expected) and all(want is None or want == have for have, want in zip(found, expected))
+
+
 def inspect(model_dir: str, config) -> Dict[str, TensorEntry]:
     """Headers of the whole folder, checked against ``config.tensor_shapes()``."""
     entries: Dict[str, TensorEntry] = {}
@@ -71,7 +78,7 @@ def inspect(model_dir: str, config) -> Dict[str, TensorEntry]:
     wrong_shape = [
         f"{name}: expected {list(shape)}, found {list(entries[name].shape)}"
         for name, shape in required.items()
-        if name in entries and tuple(entries[name].shape) != tuple(shape)]
+        if name in entries and not _fits(tuple(entries[name].shape), tuple(shape))]
     wrong_dtype = [
         f"{name}: {entries[name].dtype}" for name in required
         if name in entries and entries[name].dtype not in _FLOATS + _INTEGERS]

@@ -147,6 +147,8 @@ def random_tensors(config, seed: int, dtype: str = "bfloat16", device: str = "cp
     vector_dtype = _DTYPES[norm_dtype or dtype]
     tensors: Dict[str, torch.Tensor] = {}
     for name, shape in config.tensor_shapes().items():
+        if any(size is None for size in shape):
+            raise ValueError(f"{name}: the configuration leaves a size to the checkpoint's tensor; name it to make weights")
         # False, True / "one" (a factor near 1), "zero" (stored as factor - 1) or "identity"
         norm = config.norm_tensor(name)
         value = random_tensor(seed, name, shape, bool(norm), device)
