@@ -8,6 +8,7 @@
     python bench.py --design mekazen                              the Mekazen decoder beside Qwen3 at equal layer sizes
     python bench.py --design zitezen                              the Zitezen decoder beside Qwen3 at equal width, heads and feed-forward
     python bench.py --design sadosun                              the Sadosun decoder beside Qwen3 and Zitezen at equal width and active weights
+    python bench.py --design dimorax                              the Dimorax decoder beside Qwen3 and Sadosun at equal width and active weights
 
 Default workload: a Qwen3-0.6B-shaped model (28 layers,
 hidden 1024, 16 query and 8 key/value heads of 128, SwiGLU 3072, vocabulary
@@ -1302,6 +1303,257 @@ def design_sadosun(args):
     return 0
 
 
+# Dimorax layers at the two sizes: the delta rule's (heads, query/key groups, key channels, value columns, taps,
+# low ranks), the latent attention's (heads, unrotated and rotated key width, value width, latent rank; cached per
+# head at 128), the experts' (count, groups, kept groups, top, ff) with a shared expert of the same ff, so that
+# (top + 1) * 3 matrices of ff = the dense model's 3 * inter. Eight layers: delta rule + experts, attention + dense,
+# delta rule + dense, latent attention + experts, twice; the second attention reads the first one's keys and values.
+DIMORAX_SIZES = {"0.6b-layers": ((16, 8, 128, 128, 4, 64), (16, 64, 64, 128, 256), (12, 4, 2, 2, 1024)),
+                 "8b-layers": ((32, 8, 128, 128, 4, 256), (32, 64, 64, 128, 512), (12, 4, 2, 2, 4096))}
+
+
+def _dimorax(hidden, heads, kv_heads, dim, inter, size):
+    (dh, dg, dd, dv, taps, rank), (lh, ld, lr, lv, lrank), (count, groups, keep, top, ff) = DIMORAX_SIZES[size]
+    experts = {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": ff},
+               "router": {"experts": count, "top": top, "scale": 2.0, "groups": {"count": groups, "keep": keep}}}
+    dense = {"kind": "dense", "ff": inter}
+    delta = {"heads": dh, "kv_heads": dg, "dim": dd, "vdim": dv, "conv": taps, "ranks": {"decay": rank, "gate": rank}}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+                 "rot": {"base": 1.0e6, "dims": dim // 2,
+                         "scaling": {"factor": 16.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    through_latent = {"heads": lh, "dim": ld, "rot_dim": lr, "vdim": lv, "kv_rank": lrank, "scale": (ld + lr) ** -0.5,
+                      "rot": {"base": 1.0e4, "dims": lr}}
+    four = lambda source: [{"type": "channel_delta", "mixer": delta, "mlp": experts},
+                           {"type": "attention", "mixer": dict(attention, **({"kv_from": source} if source is not None else {})),
+                            "mlp": dense},
+                           {"type": "channel_delta", "mixer": delta, "mlp": dense},
+                           {"type": "latent_attention", "mixer": through_latent, "mlp": experts}]
+    return {"architecture": "Dimorax", "vocab": DESIGN_VOCAB, "width": hidden, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "layers": (four(None) + four(1))[:DESIGN_LAYERS]}
+
+
+def design_dimorax(args):
+    """Prompt and decode throughput of the Dimorax decoder beside the Qwen3
+    decoder (equal width, heads and active feed-forward weights) and the
+    Sadosun decoder (the other model with a recurrence, attention with a sink
+    and routed experts), random weights, bfloat16, 8 layers; then each kernel
+    the design adds beside the like kernel of those models: bytes that must
+    move over time against the measured copy bandwidth, or arithmetic over
+    time against the measured bf16 matrix peak. One JSON line."""
+    import numpy as np
+    import torch
+    from metallix_b200 import ops, parse_config
+    from metallix_b200.config.spec import PartSpec
+    from metallix_b200.parts.registry import Runtime, WeightStore, build_part
+
+    peak, peak_source = peaks()
+    warmup, steps = max(args.warmup, 3), min(max(args.steps, 1), 64)
+    rng = np.random.default_rng(0)
+    out = {"design": "dimorax", "beside": ["qwen3", "sadosun"], "dtype": "bf16", "layers": DESIGN_LAYERS,
+           "vocab": DESIGN_VOCAB, "prompt_len": args.prompt_len, "peaks": peak_source, "sizes": {}}
+    for size, (hidden, heads, kv_heads, dim, inter) in ({} if args.kernels_only else DESIGN_SIZES).items():
+        configs = {"dimorax": parse_config(_dimorax(hidden, heads, kv_heads, dim, inter, size)),
+                   "qwen3": parse_config(dict(_qwen3(DESIGN_LAYERS, hidden, heads, kv_heads, inter, False),
+                                              vocab_size=DESIGN_VOCAB, head_dim=dim)),
+                   "sadosun": parse_config(_sadosun(hidden, heads, kv_heads, dim, inter, size, args.context))}
+        out["sizes"][size] = {family: _engine_numbers(config, args, peak, rng, warmup, steps)
+                              for family, config in configs.items()}
+
+    def measure(function):
+        for _ in range(3):
+            function()
+        flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+        times = []
+        for _ in range(7):
+            flush.zero_()    # a buffer larger than L2 between the timed launches
+            times.append(timed(torch, "cuda", lambda _: function(), 1))
+        return statistics.median(times)
+
+    def gbs(bytes_moved, function):
+        ms = measure(function)
+        return {"us": ms * 1e3, "gb_s": bytes_moved / (ms * 1e-3) / 1e9,
+                "frac_of_copy_bandwidth": bytes_moved / (ms * 1e-3) / 1e9 / peak["hbm_gbs"]}
+
+    def tflops(flops, function):
+        ms = measure(function)
+        return {"us": ms * 1e3, "tflop_s": flops / (ms * 1e-3) / 1e12,
+                "frac_of_bf16_matrix_peak": flops / (ms * 1e-3) / 1e12 / peak["bf16_tflops"]}
+
+    ops.require_cuda()
+    kernels = {}
+    size = "8b-layers"
+    hidden, heads, kv_heads, dim, inter = DESIGN_SIZES[size]
+    (dh, dg, dd, dv, taps, rank), _, (count, groups, keep, top, ff) = DIMORAX_SIZES[size]
+    bf16, f32 = torch.bfloat16, torch.float32
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+    normal = lambda *shape: torch.randn(*shape, device="cuda")
+    prompt = args.prompt_len
+    runtime = Runtime(device=torch.device("cuda"), dtype=bf16, max_positions=args.context, gemm_backend=args.gemm)
+
+    def weights_of(shapes):
+        return WeightStore({name: (normal(*shape) * 0.02).to(bf16) for name, shape in shapes.items()})
+
+    # ---- what the sublayers read: the sum of two results and both norms beside the sum of one and one norm
+    for tokens in (8, prompt * 4):
+        x, a, b = normal(tokens, hidden), normal(tokens, hidden).to(bf16), normal(tokens, hidden)
+        ones = torch.ones(hidden, device="cuda")
+        kernels[f"sublayer_input_{tokens}"] = {
+            "dimorax: x += m (a + b); two norms of x": gbs(
+                tokens * hidden * (4 + 4 + 2 + 4 + 2 + 2), lambda: ops.pair_add_rmsnorm(x, a, b, 0.5, ones, ones, 1e-6, bf16)),
+            "qwen3: x += d; y = norm(x)": gbs(tokens * hidden * (4 + 4 + 2 + 2), lambda: ops.add_rmsnorm(x, a, ones, 1e-6, bf16))}
+        width = (heads + 2 * kv_heads) * dim
+        product, bias = normal(tokens, width), normal(width)
+        kernels[f"projection_bias_{tokens}"] = {
+            "dimorax: the float32 product plus its bias, rounded once": gbs(tokens * width * (4 + 2),
+                                                                          lambda: ops.add_bias(product, bias, bf16))}
+
+    # ---- the feed-forward: gated experts chosen within groups, and a shared one, beside Sadosun's and the dense one
+    names = {f"m.e{e}.{which}": (hidden, ff) if which == "down" else (ff, hidden) for e in range(count)
+             for which in ("gate", "up", "down")}
+    names.update({"m.router": (count, hidden), "m.shared.gate": (ff, hidden), "m.shared.up": (ff, hidden),
+                  "m.shared.down": (hidden, ff), "m.shared.sg": (1, hidden)})
+    store = weights_of(names)
+    store._tensors["m.correction"] = torch.zeros(count, device="cuda")
+    routed = build_part("feed_forward", PartSpec("routed_experts", {
+        "hidden_size": hidden, "intermediate_size": ff, "experts": count, "identity": 0, "top": top, "activation": "swiglu",
+        "scores": "sigmoid", "scale": 2.0, "groups": (groups, keep), "gate_proj": "m.e{}.gate", "up_proj": "m.e{}.up",
+        "down_proj": "m.e{}.down", "router": "m.router", "correction": "m.correction", "shared_gate": "m.shared.sg",
+        "shared": PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": ff, "gate_proj": "m.shared.gate",
+                                      "up_proj": "m.shared.up", "down_proj": "m.shared.down", "activation": "silu"})}),
+        store, runtime)
+    (_, _, _, _), (s_count, s_identity, s_top, s_ff), _, _ = SADOSUN_SIZES[size]
+    names = {f"s.e{e}.{which}": (s_ff, hidden) if which == "up" else (hidden, s_ff) for e in range(s_count) for which in ("up", "down")}
+    names.update({"s.router": (s_count + s_identity, hidden)})
+    store = weights_of(names)
+    store._tensors["s.correction"] = torch.zeros(s_count + s_identity, device="cuda")
+    ungated = build_part("feed_forward", PartSpec("routed_experts", {
+        "hidden_size": hidden, "intermediate_size": s_ff, "experts": s_count, "identity": s_identity, "top": s_top,
+        "activation": "relu_squared", "up_proj": "s.e{}.up", "down_proj": "s.e{}.down", "router": "s.router",
+        "correction": "s.correction"}), store, runtime)
+    dense = {act: build_part("feed_forward", PartSpec("swiglu", {
+        "hidden_size": hidden, "intermediate_size": inter, "gate_proj": "g", "up_proj": "u", "down_proj": "d",
+        "activation": act}), weights_of({"g": (inter, hidden), "u": (inter, hidden), "d": (hidden, inter)}), runtime)
+        for act in ("silu", "gelu_tanh")}
+    del store
+    for tokens in (8, prompt * 4):
+        h = normal(tokens, hidden).to(bf16)
+        logits = routed.router.forward(h, out_dtype=f32)
+        chosen = ops.route_experts(logits[:, :count], routed.correction, count, top, scores="sigmoid", groups=(groups, keep))[0]
+        distinct = int(torch.unique(chosen).numel())
+        s_chosen = ops.route_experts(ungated.router.forward(h, out_dtype=f32), ungated.correction, s_count, s_top)[0]
+        s_real = s_chosen[s_chosen < s_count]
+        s_pairs, s_distinct = int(s_real.numel()), int(torch.unique(s_real).numel())
+        label = f"feed_forward_{tokens}"
+        if tokens == 8:     # a decode step: the weights that must be read
+            kernels[label] = {
+                "dimorax: router, choice, %d distinct gated experts of %d, the shared one" % (distinct, count): gbs(
+                    (distinct + 1) * 3 * ff * hidden * 2 + (count + 1) * hidden * 2, lambda: routed.forward(h, None)),
+                "sadosun: router, choice, %d distinct experts of %d" % (s_distinct, s_count): gbs(
+                    s_distinct * 2 * s_ff * hidden * 2 + (s_count + s_identity) * hidden * 2, lambda: ungated.forward(h, None)),
+                "qwen3: gate, up, silu, down": gbs(3 * inter * hidden * 2, lambda: dense["silu"].forward(h, None)),
+                "dimorax: gate, up, gelu, down": gbs(3 * inter * hidden * 2, lambda: dense["gelu_tanh"].forward(h, None))}
+        else:               # a prompt: the products that must be made
+            kernels[label] = {
+                "dimorax: router, choice, the chosen gated experts, the shared one": tflops(
+                    (top + 1) * tokens * 6.0 * ff * hidden + tokens * 2.0 * (count + 1) * hidden, lambda: routed.forward(h, None)),
+                "sadosun: router, choice, the chosen experts": tflops(
+                    s_pairs * 4.0 * s_ff * hidden + tokens * 2.0 * (s_count + s_identity) * hidden, lambda: ungated.forward(h, None)),
+                "qwen3: gate, up, silu, down": tflops(tokens * 6.0 * inter * hidden, lambda: dense["silu"].forward(h, None)),
+                "dimorax: gate, up, gelu, down": tflops(tokens * 6.0 * inter * hidden, lambda: dense["gelu_tanh"].forward(h, None))}
+    del routed, ungated, dense
+
+    # ---- a decode step's mixer over 8 requests: a state per request against cached keys and values
+    batch, context = 8, prompt
+    rows, one_each = ints(range(batch)), ints([1] * batch)
+
+    def delta_inputs(tokens):
+        return (normal(tokens, 2 * dg * dd + dh * dv).to(bf16), normal(tokens, dh), normal(tokens, dh * dd))
+
+    step_bias, rate = normal(dh * dd) - 3.0, torch.exp(normal(dh) * 0.3)
+    qkv, beta, step = delta_inputs(batch)
+    delta_state = torch.zeros(batch, dh, dd, dv, device="cuda")
+    kernels["decode_step_mixer_8_requests"] = {
+        "dimorax: delta rule, state read and written": gbs(
+            2 * delta_state.numel() * 4, lambda: ops.delta_rule(qkv, (0, dg * dd, 2 * dg * dd), beta, step, step_bias, rate,
+                                                                delta_state, rows, one_each, rows, dh, dg, dd, dv))}
+    (inner, states, s_rank, _), _, _, _ = SADOSUN_SIZES[size]
+    a = -torch.exp(normal(inner, states) * 0.5)
+    s_bias, skip = normal(inner) - 3.0, normal(inner)
+
+    def scan_inputs(tokens):
+        return normal(tokens, 2 * inner).to(bf16), normal(tokens, s_rank + 2 * states).to(bf16), normal(tokens, inner)
+
+    both, picked, s_step = scan_inputs(batch)
+    scan_state = torch.zeros(batch, inner, states, device="cuda")
+    kernels["decode_step_mixer_8_requests"]["sadosun: selective scan, state read and written"] = gbs(
+        2 * scan_state.numel() * 4 + a.numel() * 4,
+        lambda: ops.selective_scan(both[:, :inner], s_step, s_bias, a, picked[:, s_rank:s_rank + states],
+                                   picked[:, s_rank + states:], skip, both[:, inner:], scan_state, rows, one_each, rows))
+    H, D, V = ZITEZEN_SIZES[size][0]
+    width = 2 * H * D + 2 * H * V + 2 * H
+    proj = normal(batch, width) * 0.1
+    memory_state = torch.zeros(batch, ops.mlstm_state_values(H, D, V), device="cuda")
+    zeros = torch.zeros(H, device="cuda")
+    offsets = (0, H * D, 2 * H * D, 2 * H * D + 2 * H * V, 2 * H * D + 2 * H * V + H)
+    kernels["decode_step_mixer_8_requests"]["zitezen: matrix memory, state read and written"] = gbs(
+        2 * memory_state.numel() * 4, lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 10.0, memory_state, rows,
+                                                             one_each, rows, H, D, V))
+    pages = batch * (-(-context // 16))
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").view(batch, -1)
+    positions = ints([context - 1] * batch)
+    cache = normal(pages, 2, kv_heads, 16, dim).to(bf16)
+    q = normal(batch, heads, dim).to(bf16)
+    attended = torch.empty_like(q)
+    sinks = normal(heads)
+    kernels["decode_step_mixer_8_requests"]["qwen3: split-key attention over %d cached positions" % context] = gbs(
+        cache.numel() * 2, lambda: ops.paged_attention_decode(q, cache, attended, table, rows, rows, positions, dim ** -0.5,
+                                                              context))
+    kernels["decode_step_mixer_8_requests"]["dimorax: the same with capped scores and a sink per head"] = gbs(
+        cache.numel() * 2, lambda: ops.paged_attention_decode(q, cache, attended, table, rows, rows, positions, dim ** -0.5,
+                                                              context, softcap=30.0, sink=sinks))
+
+    # ---- a prompt in one step
+    tokens = prompt
+    qkv, beta, step = delta_inputs(tokens)
+    delta_state.zero_()
+    one_row, length = ints([0]), ints([tokens])
+    kernels[f"prompt_mixer_{tokens}"] = {
+        "dimorax: delta rule of one request (rows read and written)": gbs(
+            tokens * ((2 * dg * dd + dh * dv) * 2 + dh * 4 + dh * dd * 4 + dh * dv * 4),
+            lambda: ops.delta_rule(qkv, (0, dg * dd, 2 * dg * dd), beta, step, step_bias, rate, delta_state, one_row, length,
+                                   one_row, dh, dg, dd, dv))}
+    both, picked, s_step = scan_inputs(tokens)
+    scan_state.zero_()
+    kernels[f"prompt_mixer_{tokens}"]["sadosun: selective scan of one request (rows read and written)"] = gbs(
+        tokens * inner * (2 + 4 + 2 + 2) + tokens * 2 * states * 2,
+        lambda: ops.selective_scan(both[:, :inner], s_step, s_bias, a, picked[:, s_rank:s_rank + states],
+                                   picked[:, s_rank + states:], skip, both[:, inner:], scan_state, one_row, length, one_row))
+    proj = normal(tokens, width) * 0.1
+    memory_state.zero_()
+    kernels[f"prompt_mixer_{tokens}"]["zitezen: matrix memory of one request, in chunks (rows read and written)"] = gbs(
+        tokens * (width * 4 + H * V * 4), lambda: ops.mlstm_scan(proj, offsets, zeros, zeros, 10.0, memory_state, one_row,
+                                                                 length, one_row, H, D, V, longest=tokens))
+    pages = -(-tokens // 16)
+    table = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, -1)
+    positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    cache = normal(pages, 2, kv_heads, 16, dim).to(bf16)
+    q = normal(tokens, heads, dim).to(bf16)
+    attended = torch.empty_like(q)
+    flops = 4.0 * dim * heads * tokens * (tokens + 1) / 2
+    tile = ops.flash_prefill_tile()
+    starts = list(range(0, tokens, tile))[::-1]
+    tiles = (ints([0] * len(starts)), ints(starts), ints([min(tile, tokens - s) for s in starts]))
+    kernels[f"prompt_mixer_{tokens}"]["qwen3: tensor-core attention"] = tflops(
+        flops, lambda: ops.flash_prefill(q, cache, attended, table, *tiles, positions, dim ** -0.5, longest_context=tokens))
+    kernels[f"prompt_mixer_{tokens}"]["dimorax: the same with capped scores and a sink per head"] = tflops(
+        flops, lambda: ops.flash_prefill(q, cache, attended, table, *tiles, positions, dim ** -0.5, longest_context=tokens,
+                                         softcap=30.0, sink=sinks))
+    ops.check_status("cuda")
+    out["kernels"] = kernels
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
@@ -1340,7 +1592,7 @@ def main():
     parser.add_argument("--kernel", default="both", choices=("both", "tcgen05", "mma"))
     parser.add_argument("--page-tokens", type=int, default=16, help="workloads: tokens per cache page")
     parser.add_argument("--max-context", type=int, default=0, help="workloads: the engine's context limit")
-    parser.add_argument("--design", choices=("mekazen", "zitezen", "sadosun"),
+    parser.add_argument("--design", choices=("mekazen", "zitezen", "sadosun", "dimorax"),
                         help="another decoder design beside Qwen3 at equal layer sizes, and its kernels beside their like")
     parser.add_argument("--chunk", type=int, default=0, help="--design: positions per chunk of the mask (0: the context)")
     parser.add_argument("--kernels-only", action="store_true",
@@ -1360,6 +1612,8 @@ def main():
         return design_zitezen(args)
     if args.design == "sadosun" and not args.workload:
         return design_sadosun(args)
+    if args.design == "dimorax" and not args.workload:
+        return design_dimorax(args)
     if args.design and not args.workload:
         return design(args)
     if args.workload:

@@ -100,7 +100,7 @@ def seen_keys(count, window=0):
 # ---------------------------------------------------------------- attention
 def keys_and_values(h, tensors, base, mixer):
     """Rotated keys ``[T, G, D]`` and values ``[T, G, Dv]`` of an attention layer that has projections."""
-    count, G, D, Dv = h.shape[0], mixer["kv_heads"], mixer["dim"], mixer["vdim"]
+    count, G, D, Dv = h.shape[0], mixer.get("kv_heads") or mixer["heads"], mixer["dim"], mixer.get("vdim") or mixer["dim"]
     k = (h @ tensors[f"{base}.k"].T + tensors[f"{base}.k.b"]).reshape(count, G, D)
     v = (h @ tensors[f"{base}.v"].T + tensors[f"{base}.v.b"]).reshape(count, G, Dv)
     rot = mixer.get("rot")
@@ -113,7 +113,8 @@ def biased_attention(h, tensors, base, mixer, keys=None, values=None, weights_ou
     """Grouped-query attention with biased projections, rotation of halves,
     capped scores, a causal mask and a learned sink per head. ``keys`` /
     ``values``: another layer's, for a layer without projections of its own."""
-    count, H, G, D, Dv = h.shape[0], mixer["heads"], mixer["kv_heads"], mixer["dim"], mixer["vdim"]
+    count, H, D = h.shape[0], mixer["heads"], mixer["dim"]
+    G, Dv = mixer.get("kv_heads") or H, mixer.get("vdim") or D
     q = (h @ tensors[f"{base}.q"].T + tensors[f"{base}.q.b"]).reshape(count, H, D)
     rot = mixer.get("rot")
     if rot:
@@ -138,7 +139,8 @@ def biased_attention(h, tensors, base, mixer, keys=None, values=None, weights_ou
 def latent_attention(h, tensors, base, mixer, eps, weights_out=None, use_sink=True):
     """Keys and values from one normed latent per position plus one rotated
     key part that all heads share; a sliding window; a learned sink per head."""
-    count, H, D, R, Dv, r = h.shape[0], mixer["heads"], mixer["dim"], mixer["rot_dim"], mixer["vdim"], mixer["kv_rank"]
+    count, H, D, R, r = h.shape[0], mixer["heads"], mixer["dim"], mixer["rot_dim"], mixer["kv_rank"]
+    Dv = mixer.get("vdim") or D
     positions = np.arange(count)
     rot = mixer["rot"]
     q = (h @ tensors[f"{base}.q"].T).reshape(count, H, D + R)
@@ -194,7 +196,8 @@ def channel_delta(h, tensors, base, mixer, eps, carry=None):
     """The gated delta rule with one decay per head and key channel.
     ``carry`` = (conv inputs of q, k, v, states [H, D, Dv]) from an earlier
     piece; returns the output and the new carry."""
-    count, H, G, D, Dv = h.shape[0], mixer["heads"], mixer["kv_heads"], mixer["dim"], mixer["vdim"]
+    count, H, D = h.shape[0], mixer["heads"], mixer["dim"]
+    G, Dv = mixer.get("kv_heads") or H, mixer.get("vdim") or D
     before = carry if carry is not None else (None, None, None, [None] * H)
     q, q_in = causal_conv(h @ tensors[f"{base}.q"].T, tensors[f"{base}.q.conv"], before[0])
     k, k_in = causal_conv(h @ tensors[f"{base}.k"].T, tensors[f"{base}.k.conv"], before[1])
