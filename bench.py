@@ -1467,7 +1467,7 @@ def design_dimorax(args):
     rows, one_each = ints(range(batch)), ints([1] * batch)
 
     def delta_inputs(tokens):
-        return (normal(tokens, 2 * dg * dd + dh * dv).to(bf16), normal(tokens, dh), normal(tokens, dh * dd))
+        return (normal(tokens, 2 * dg * dd + dh * dv).to(bf16), normal(tokens, dh).to(bf16), normal(tokens, dh * dd))
 
     step_bias, rate = normal(dh * dd) - 3.0, torch.exp(normal(dh) * 0.3)
     qkv, beta, step = delta_inputs(batch)
@@ -1519,7 +1519,7 @@ def design_dimorax(args):
     one_row, length = ints([0]), ints([tokens])
     kernels[f"prompt_mixer_{tokens}"] = {
         "dimorax: delta rule of one request (rows read and written)": gbs(
-            tokens * ((2 * dg * dd + dh * dv) * 2 + dh * 4 + dh * dd * 4 + dh * dv * 4),
+            tokens * ((2 * dg * dd + dh * dv) * 2 + dh * 2 + dh * dd * 4 + dh * dv * 4),
             lambda: ops.delta_rule(qkv, (0, dg * dd, 2 * dg * dd), beta, step, step_bias, rate, delta_state, one_row, length,
                                    one_row, dh, dg, dd, dv))}
     both, picked, s_step = scan_inputs(tokens)

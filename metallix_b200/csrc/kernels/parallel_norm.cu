@@ -92,6 +92,23 @@ add_bias_kernel(const TIn* __restrict__ in, long long ldi, const float* __restri
   out[t * ldo + c] = from_float<TOut>(to_float(in[t * ldi + c]) + bias[c]);
 }
 
+// The same, eight columns a thread (width a multiple of 8, rows and bias on 16-byte boundaries).
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256)
+add_bias_by8_kernel(const TIn* __restrict__ in, long long ldi, const float* __restrict__ bias, TOut* __restrict__ out,
+                    long long ldo, int width, long long groups) {
+  const long long index = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (index >= groups) return;
+  const int per_row = width / 8;
+  const long long t = index / per_row;
+  const int c = static_cast<int>(index - t * per_row) * 8;
+  const float4 lo = pn_load4(in + t * ldi + c, sizeof(TIn) == 4 ? kF32 : kBF16, 0);
+  const float4 hi = pn_load4(in + t * ldi + c + 4, sizeof(TIn) == 4 ? kF32 : kBF16, 0);
+  const float4 b_lo = *reinterpret_cast<const float4*>(bias + c), b_hi = *reinterpret_cast<const float4*>(bias + c + 4);
+  pn_store4(out + t * ldo + c, make_float4(lo.x + b_lo.x, lo.y + b_lo.y, lo.z + b_lo.z, lo.w + b_lo.w));
+  pn_store4(out + t * ldo + c + 4, make_float4(hi.x + b_hi.x, hi.y + b_hi.y, hi.z + b_hi.z, hi.w + b_hi.w));
+}
+
 }  // namespace mxb
 
 using namespace mxb;
@@ -128,6 +145,19 @@ MXB_API int mxb_add_bias(const void* in, long long ldi, int in_dtype, const floa
                          int out_dtype, int tokens, int width, cudaStream_t stream) {
   const long long total = static_cast<long long>(tokens) * width;
   if (total <= 0) return 0;
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (width % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && aligned(in) && aligned(out) && aligned(bias)) {
+    const long long groups = total / 8;
+    const unsigned by8 = static_cast<unsigned>((groups + 255) / 256);
+#define BY8(TI, TO) add_bias_by8_kernel<TI, TO><<<by8, 256, 0, stream>>>(static_cast<const TI*>(in), ldi, bias, \
+                                                                          static_cast<TO*>(out), ldo, width, groups)
+    if (in_dtype == kF32 && out_dtype == kF32) BY8(float, float);
+    else if (in_dtype == kF32 && out_dtype == kBF16) BY8(float, __nv_bfloat16);
+    else if (in_dtype == kBF16 && out_dtype == kBF16) BY8(__nv_bfloat16, __nv_bfloat16);
+    else return static_cast<int>(cudaErrorInvalidValue);
+#undef BY8
+    return static_cast<int>(cudaGetLastError());
+  }
   const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
 #define LAUNCH(TI, TO) add_bias_kernel<TI, TO><<<blocks, 256, 0, stream>>>(static_cast<const TI*>(in), ldi, bias, \
                                                                              static_cast<TO*>(out), ldo, width, total)

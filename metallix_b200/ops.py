@@ -863,8 +863,8 @@ def delta_rule(qkv: torch.Tensor, offsets, beta: torch.Tensor, step: torch.Tenso
     tokens. ``qkv`` ``[tokens, columns]`` holds, from the column ``offsets``
     (q, k, v) on, groups * dim queries and keys and heads * vdim values (after
     their convolution and activation); head h reads group h // (heads / groups).
-    ``beta`` float32 ``[tokens, heads]`` (a view of a wider tensor will do) are
-    the pre-activations of the write strength, ``step`` float32
+    ``beta`` ``[tokens, heads]`` of qkv's type (a view of a wider tensor will do)
+    are the pre-activations of the write strength, ``step`` float32
     ``[tokens, heads * dim]`` those of the step size, to which ``step_bias``
     ``[heads * dim]`` is added; ``rate`` ``[heads]`` is positive. Per head:
     q and k become unit vectors (q times dim^-1/2), g = exp(-rate softplus(step
@@ -876,8 +876,8 @@ def delta_rule(qkv: torch.Tensor, offsets, beta: torch.Tensor, step: torch.Tenso
     _need(qkv.is_cuda and qkv.dtype in _CODES and qkv.dim() == 2 and qkv.stride(1) == 1,
           "qkv must be a CUDA [tokens, columns] tensor with unit column stride")
     tokens = qkv.shape[0]
-    _need(beta.is_cuda and beta.dtype == torch.float32 and beta.dim() == 2 and beta.stride(1) == 1
-          and beta.shape == (tokens, heads), "beta must be float32 [tokens, heads]")
+    _need(beta.is_cuda and beta.dtype == qkv.dtype and beta.dim() == 2 and beta.stride(1) == 1
+          and beta.shape == (tokens, heads), "beta must be [tokens, heads] of qkv's type")
     _need(step.is_cuda and step.dtype == torch.float32 and step.dim() == 2 and step.stride(1) == 1
           and step.shape == (tokens, heads * dim), "step must be float32 [tokens, heads * dim]")
     _check(step_bias, "step_bias", (torch.float32,), 1)

@@ -226,10 +226,11 @@ class ChannelDelta:
     Each head's o over its root mean square times a weight over V (shared by
     the heads) times sigmoid((a Wg1^T) Wg2^T), then Wo. S (float32
     ``[H, D, V]``) and the convolution's last inputs are kept per request in
-    the cache's state slots. One product gives q, k, v, the write strength and
-    both low-rank inputs in float32; unit norms, decay, beta, the recurrence
-    and the head norm are float32 in both precisions; the convolution and its
-    activation hand on the compute type."""
+    the cache's state slots. One product gives q, k, v, both low-rank inputs
+    and the write strength's pre-activation; the step size's second product
+    leaves in float32; unit norms, softplus, decay, sigmoid, the recurrence and
+    the head norm are float32 in both precisions; the projections, the
+    convolution and its activation hand on the compute type."""
 
     kind = "channel_delta"
     graph_safe = True
@@ -263,12 +264,12 @@ class ChannelDelta:
         step_rank, gate_rank = weights.shape(spec["step_down_proj"])[0], weights.shape(spec["gate_down_proj"])[0]
         self.conv_channels = 2 * G * D + H * V
         stacked, self.offsets, cursor = [], {}, 0
-        for name, rows in (("q_proj", G * D), ("k_proj", G * D), ("v_proj", H * V), ("beta_proj", H),
-                           ("step_down_proj", step_rank), ("gate_down_proj", gate_rank)):
+        for name, rows in (("q_proj", G * D), ("k_proj", G * D), ("v_proj", H * V), ("step_down_proj", step_rank),
+                           ("gate_down_proj", gate_rank), ("beta_proj", H)):
             stacked.append(matrix(name, (rows, hidden)))
             self.offsets[name] = cursor
             cursor += rows
-        self.inputs = Linear.stacked(stacked, runtime)     # rows: q, k, v, write strength, step latent, gate latent
+        self.inputs = Linear.stacked(stacked, runtime)     # rows: q, k, v, step latent, gate latent, write strength
         self.step_rank, self.gate_rank = step_rank, gate_rank
         self.step_up = Linear(matrix("step_up_proj", (H * D, step_rank)), runtime)
         self.gate_up = Linear(matrix("gate_up_proj", (H * V, gate_rank)), runtime)
@@ -297,18 +298,14 @@ class ChannelDelta:
             raise ValueError("the delta-rule mixer needs its two state entries of the cache")
         rows = request_rows_of(ctx)
         H, G, D, V, at = self.heads, self.groups, self.dim, self.vdim, self.offsets
-        proj = self.inputs.forward(x, out_dtype=torch.float32)
-        qkv = proj[:, :self.conv_channels]
-        if self.dtype != torch.float32:
-            qkv = qkv.to(self.dtype)       # what the projections hand on
-        qkv = self.conv.forward(qkv, ctx, cache.members[1])
-        low = proj[:, at["step_down_proj"]:at["step_down_proj"] + self.step_rank].to(self.dtype).contiguous()
-        step = self.step_up.forward(low, out_dtype=torch.float32)
+        proj = self.inputs.forward(x)       # every later step reads column ranges of it in place
+        qkv = self.conv.forward(proj[:, :self.conv_channels], ctx, cache.members[1])
+        step = self.step_up.forward(proj[:, at["step_down_proj"]:at["step_down_proj"] + self.step_rank],
+                                    out_dtype=torch.float32)
         mixed = ops.delta_rule(qkv, (0, G * D, 2 * G * D), proj[:, at["beta_proj"]:at["beta_proj"] + H], step,
                                self.step_bias, self.rate, cache.members[0].state, rows["row_start"],
                                rows["row_length"], ctx.request_slots, H, G, D, V)
-        low = proj[:, at["gate_down_proj"]:at["gate_down_proj"] + self.gate_rank].to(self.dtype).contiguous()
-        gate = self.gate_up.forward(low, out_dtype=torch.float32)
+        gate = self.gate_up.forward(proj[:, at["gate_down_proj"]:at["gate_down_proj"] + self.gate_rank])
         return self.o.forward(ops.head_norm_gate(mixed, self.norm_weight, gate, H, self.eps, self.dtype))
 
     def weight_bytes(self) -> int:

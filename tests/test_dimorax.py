@@ -409,8 +409,10 @@ def rows_of(lengths):
 def test_delta_rule_kernel(dtype, heads, groups, dim, vdim):
     """The recurrence over request rows of unequal length in one launch (a
     single token, a padding row), continued twice from the state the launch
-    before left, against the plain rule in one piece. Decays are slow and the
-    first token's value is large, so that it still counts at the end."""
+    before left, against the plain rule in one piece. Decays are slow, the
+    first token's value is large and the last token's query is the first
+    token's key, so that what the first token wrote is what the last one
+    reads."""
     from metallix_b200 import ops
     rng = np.random.default_rng(heads * dim + vdim)
     pieces = [[23, 1, 0, 5], [1, 1, 0, 40], [9, 3, 0, 1]]
@@ -421,9 +423,12 @@ def test_delta_rule_kernel(dtype, heads, groups, dim, vdim):
     seq = []
     for total in totals:
         first = np.where(np.arange(total) == 0, 64.0, 1.0)[:, None]
-        seq.append({"q": rounded(rng.normal(size=(total, groups * dim)), dtype), "k": rounded(rng.normal(size=(total, groups * dim)), dtype),
+        q_rows, k_rows = rng.normal(size=(total, groups * dim)), rng.normal(size=(total, groups * dim))
+        if total > 30:
+            q_rows[-1] = k_rows[0]
+        seq.append({"q": rounded(q_rows, dtype), "k": rounded(k_rows, dtype),
                     "v": rounded(rng.normal(size=(total, heads * vdim)) * first, dtype),
-                    "b": rounded(rng.normal(size=(total, heads)) * 2.0, torch.float32),
+                    "b": rounded(rng.normal(size=(total, heads)) * 2.0, dtype),
                     "s": rounded(rng.normal(size=(total, heads * dim)), torch.float32)})
     state = torch.full((5, heads, dim, vdim), 3.0, device="cuda")
     for slot in slots:
@@ -434,7 +439,7 @@ def test_delta_rule_kernel(dtype, heads, groups, dim, vdim):
         starts = rows_of(lengths)
         pack = lambda key: np.concatenate([seq[row][key][done[row]:done[row] + n] for row, n in enumerate(lengths)])
         qkv = dev(np.concatenate([np.zeros((sum(lengths), 8)), pack("q"), pack("k"), pack("v")], axis=1), dtype)
-        wide = dev(np.concatenate([pack("b"), np.zeros((sum(lengths), 3))], axis=1))
+        wide = dev(np.concatenate([pack("b"), np.zeros((sum(lengths), 3))], axis=1), dtype)
         out = ops.delta_rule(qkv, (8, 8 + groups * dim, 8 + 2 * groups * dim), wide[:, :heads], dev(pack("s")), dev(bias), dev(rate),
                              state, dev(starts, torch.int32), dev(lengths, torch.int32), dev(slots, torch.int32), heads, groups, dim, vdim)
         ops.check_status("cuda")
@@ -460,7 +465,7 @@ def test_delta_rule_kernel(dtype, heads, groups, dim, vdim):
             if total > 30:       # without the first token's write the last output is another
                 again, _ = plain.delta_rule(q[1:, group], k[1:, group], s["v"][1:, head * vdim:(head + 1) * vdim],
                                             plain.sigmoid(s["b"][1:, head]), decay[1:, head])
-                assert np.abs(again[-1] - want[-1]).max() > 5 * 2e-4 * max(1.0, np.abs(want).max())
+                assert np.abs(again[-1] - want[-1]).max() > 10 * 2e-4 * max(1.0, np.abs(want).max())
 
 
 @gpu
@@ -615,7 +620,7 @@ def test_stretched_wavelengths_in_the_position_tables():
     (torch.bfloat16, 64, 8, 2, 700, 16, 150), (torch.bfloat16, 128, 4, 4, 2300, 16, 0), (torch.float32, 64, 4, 2, 500, 8, 129),
     (torch.float32, 24, 3, 1, 200, 4, 0), (torch.bfloat16, 40, 6, 3, 300, 8, 37)])
 def test_a_learned_sink_per_head_in_every_attention_kernel(dtype, head_dim, heads, kv_heads, context, page, window):
-    """Every query head has a sink score of its own (between -4 and 4) in the
+    """Every query head has a sink score of its own (of the size of all its keys' weights together) in the
     general kernel, the split-key decode kernels and both tensor-core prompt
     kernels. One query looks for the oldest key its window still holds and one
     for the key just outside it; with no window one looks hundreds of
@@ -623,7 +628,7 @@ def test_a_learned_sink_per_head_in_every_attention_kernel(dtype, head_dim, head
     from metallix_b200 import ops
     rng = np.random.default_rng(head_dim + context)
     scale, tail = 0.15, 24
-    sink = rounded(rng.uniform(-4.0, 4.0, size=heads), torch.float32)
+    sink = rounded(rng.uniform(-3.0, 3.0, size=heads) + np.log(window or context), torch.float32)   # of the size of the keys' sum
     keys = rng.normal(size=(context, kv_heads, head_dim)) * 0.5
     values = rng.normal(size=(context, kv_heads, head_dim))
     q = rng.normal(size=(tail, heads, head_dim)) * 0.5
@@ -659,7 +664,7 @@ def test_a_learned_sink_per_head_in_every_attention_kernel(dtype, head_dim, head
             want[t, h] = w[0] @ v_all[low:p + 1, h]
             plain_softmax[t, h] = plain.sink_softmax(s[h:h + 1], np.ones_like(s[h:h + 1], dtype=bool), None)[0] @ v_all[low:p + 1, h]
     tolerance = 3e-5 if dtype == torch.float32 else 3e-2
-    assert np.abs(want - plain_softmax).max() > 5 * tolerance      # the sinks take a share that shows
+    assert np.abs(want - plain_softmax).max() > 10 * tolerance      # the sinks take a share that shows
     tables, sinks = dev(order[None, :], torch.int32), dev(sink)
     out = torch.empty((tail, heads, head_dim), dtype=dtype, device="cuda")
     ops.paged_attention_tile(dev(q, dtype), pool, out, tables, dev([0, 0], torch.int32), dev([0, 16], torch.int32),
