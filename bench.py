@@ -666,6 +666,9 @@ def workload(args):
         if args.design == "zitezen":   # its layers come in fours: the first `layers` of them
             other = _zitezen(hidden, heads, kv_heads, dim, inter, {"0.6b": "0.6b-layers", "8b": "8b-layers"}[args.shape])
             config = parse_config(dict(other, layers=(other["layers"] * layers)[:layers]))
+        elif args.design == "dimorax":   # its layers come in fours; a layer that reads another's keys has its source among them
+            other = _dimorax(hidden, heads, kv_heads, dim, inter, {"0.6b": "0.6b-layers", "8b": "8b-layers"}[args.shape])
+            config = parse_config(dict(other, layers=other["layers"][:4] if layers <= 4 else other["layers"][:layers]))
         elif args.design == "sadosun":   # its layers come in twos
             other = _sadosun(hidden, heads, kv_heads, dim, inter, {"0.6b": "0.6b-layers", "8b": "8b-layers"}[args.shape],
                              args.chunk or 4096)
@@ -1471,11 +1474,11 @@ def design_dimorax(args):
 
     step_bias, rate = normal(dh * dd) - 3.0, torch.exp(normal(dh) * 0.3)
     qkv, beta, step = delta_inputs(batch)
-    delta_state = torch.zeros(batch, dh, dd, dv, device="cuda")
+    delta_state = torch.zeros(batch, dh, dv, dd, device="cuda")
     kernels["decode_step_mixer_8_requests"] = {
         "dimorax: delta rule, state read and written": gbs(
             2 * delta_state.numel() * 4, lambda: ops.delta_rule(qkv, (0, dg * dd, 2 * dg * dd), beta, step, step_bias, rate,
-                                                                delta_state, rows, one_each, rows, dh, dg, dd, dv))}
+                                                                delta_state, rows, one_each, rows, dh, dg, dd, dv, longest=1))}
     (inner, states, s_rank, _), _, _, _ = SADOSUN_SIZES[size]
     a = -torch.exp(normal(inner, states) * 0.5)
     s_bias, skip = normal(inner) - 3.0, normal(inner)

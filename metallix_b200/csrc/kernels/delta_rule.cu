@@ -79,13 +79,14 @@ delta_rule_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
   }
   // this thread's quarter of its columns of S
   float s[COLS][DPT];
+  // In memory a column's channels lie side by side ([heads, vdim, dim]): a lane's share is one run of DPT values.
   float* column_state = state + static_cast<long long>(slot) * slot_stride +
-                        (static_cast<long long>(head) * dim) * vdim + column;
+                        (static_cast<long long>(head) * vdim + column) * dim + part * DPT;
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
     const int d = part * DPT + i;
 #pragma unroll
-    for (int c = 0; c < COLS; ++c) s[c][i] = live[c] && d < dim ? column_state[static_cast<long long>(d) * vdim + c] : 0.0f;
+    for (int c = 0; c < COLS; ++c) s[c][i] = live[c] && d < dim ? column_state[static_cast<long long>(c) * dim + i] : 0.0f;
   }
   // What the next batch needs from memory, asked for a batch ahead: the raw q, k and step size of the token
   // this warp prepares, its write strength, and this thread's value of every token of the batch.
@@ -210,7 +211,7 @@ delta_rule_kernel(const T* __restrict__ qkv, long long ld, int q_off, int k_off,
     const int d = part * DPT + i;
 #pragma unroll
     for (int c = 0; c < COLS; ++c)
-      if (live[c] && d < dim) column_state[static_cast<long long>(d) * vdim + c] = s[c][i];
+      if (live[c] && d < dim) column_state[static_cast<long long>(c) * dim + i] = s[c][i];
   }
 }
 
@@ -225,14 +226,15 @@ MXB_API int mxb_delta_rule_max_dim() { return 256; }
 // heads * vdim values (after their convolution and activation). beta_pre: [tokens, ldb] of `dtype`, one
 // pre-activation per head from column b_off on. step_pre: float32 [tokens, lds] with heads * dim step
 // pre-activations; step_bias: float32 [heads * dim]; rate: float32 [heads] (positive). state: float32
-// [num_slots, heads, dim, vdim], rows slot_stride values apart, advanced in place. Row r brings row_length[r]
+// [num_slots, heads, vdim, dim] (S transposed: a value column's key channels side by side), rows slot_stride
+// values apart, advanced in place. Row r brings row_length[r]
 // tokens (0: a padding row, nothing is read or written) from packed token row_start[r] on and owns slot
-// request_slots[r]. out: float32 [tokens, heads * vdim].
+// request_slots[r]. out: float32 [tokens, heads * vdim]. longest: the most tokens any row brings, 0 if unknown.
 MXB_API int mxb_delta_rule(const void* qkv, long long ld, int q_off, int k_off, int v_off, const void* beta_pre,
                            long long ldb, int b_off, const float* step_pre, long long lds, const float* step_bias,
                            const float* rate, float* state, long long slot_stride, int num_slots,
                            const int* row_start, const int* row_length, const int* request_slots, float* out,
-                           int rows, int heads, int groups, int dim, int vdim, int dtype, int* status,
+                           int rows, int heads, int groups, int dim, int vdim, int dtype, int longest, int* status,
                            cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (heads <= 0 || groups <= 0 || heads % groups != 0 || dim <= 0 || dim > mxb_delta_rule_max_dim() || vdim <= 0)
@@ -243,7 +245,9 @@ MXB_API int mxb_delta_rule(const void* qkv, long long ld, int q_off, int k_off, 
   const int per_lane = dim <= 16 ? 4 : (dim <= 128 ? 8 : 16);
   const int step = 32 / lanes;                                   // columns of a warp
   int columns = ((vdim + step - 1) / step) * step;
-  const int most = 512 / lanes;
+  // A step of single tokens (`longest`, the most tokens of any row, if the caller knows it; 0: unknown) is one
+  // chain of trips to memory per block: small blocks, several of them resident on an SM, overlap their chains.
+  const int most = (longest > 0 && longest < 8 ? 128 : 512) / lanes;
   if (columns > most) columns = most;
   while (columns > 2 * step && columns >= 32 &&
          static_cast<long long>(rows) * heads * ((vdim + columns - 1) / columns) < 128)

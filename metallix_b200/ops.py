@@ -53,7 +53,7 @@ _SIGNATURES = {
     "mxb_add_bias": [_P, _L, _I, _P, _P, _L, _I, _I, _I, _P],
     "mxb_delta_rule_max_dim": [],
     "mxb_delta_rule": [_P, _L, _I, _I, _I, _P, _L, _I, _P, _L, _P, _P, _P, _L, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I,
-                       _I, _P, _P],
+                       _I, _I, _P, _P],
     "mxb_add_cast": [_P, _P, _I, _P, _I, _L, _P],
     "mxb_gelu_gate_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     "mxb_stream_mix": [_P, _P, _P, _L, _L, _F, _F, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
@@ -858,7 +858,8 @@ def delta_rule_max_dim() -> int:
 
 def delta_rule(qkv: torch.Tensor, offsets, beta: torch.Tensor, step: torch.Tensor, step_bias: torch.Tensor,
                rate: torch.Tensor, state: torch.Tensor, row_start: torch.Tensor, row_length: torch.Tensor,
-               request_slots: torch.Tensor, heads: int, groups: int, dim: int, vdim: int) -> torch.Tensor:
+               request_slots: torch.Tensor, heads: int, groups: int, dim: int, vdim: int,
+               longest: int = 0) -> torch.Tensor:
     """The gated delta rule with a decay per head and key channel over a step's
     tokens. ``qkv`` ``[tokens, columns]`` holds, from the column ``offsets``
     (q, k, v) on, groups * dim queries and keys and heads * vdim values (after
@@ -869,10 +870,11 @@ def delta_rule(qkv: torch.Tensor, offsets, beta: torch.Tensor, step: torch.Tenso
     ``[heads * dim]`` is added; ``rate`` ``[heads]`` is positive. Per head:
     q and k become unit vectors (q times dim^-1/2), g = exp(-rate softplus(step
     + bias)), S <- g S (by rows); u = sigmoid(beta) (v - S^T k); S <- S + k u^T;
-    o = S^T q. ``state`` float32 ``[slots, heads, dim, vdim]`` is advanced in
-    place; request row r brings ``row_length[r]`` tokens from packed token
+    o = S^T q. ``state`` float32 ``[slots, heads, vdim, dim]`` (S transposed: a
+    value column's key channels side by side) is advanced in place; request row r brings ``row_length[r]`` tokens from packed token
     ``row_start[r]`` on (0: a padding row) and owns slot ``request_slots[r]``.
-    Returns float32 ``[tokens, heads * vdim]``."""
+    Returns float32 ``[tokens, heads * vdim]``. ``longest``: the most tokens of
+    a row if known (a step of single tokens gets smaller blocks)."""
     _need(qkv.is_cuda and qkv.dtype in _CODES and qkv.dim() == 2 and qkv.stride(1) == 1,
           "qkv must be a CUDA [tokens, columns] tensor with unit column stride")
     tokens = qkv.shape[0]
@@ -884,7 +886,7 @@ def delta_rule(qkv: torch.Tensor, offsets, beta: torch.Tensor, step: torch.Tenso
     _check(rate, "rate", (torch.float32,), 1)
     _need(step_bias.numel() == heads * dim and rate.numel() == heads, "step_bias or rate has the wrong size")
     _check(state, "state", (torch.float32,), 4)
-    _need(state.shape[1:] == (heads, dim, vdim), f"state must be [slots, {heads}, {dim}, {vdim}]")
+    _need(state.shape[1:] == (heads, vdim, dim), f"state must be [slots, {heads}, {vdim}, {dim}]")
     _need(heads % groups == 0 and 0 < dim <= delta_rule_max_dim(), "the head layout does not fit")
     for name, tensor in (("row_start", row_start), ("row_length", row_length), ("request_slots", request_slots)):
         _check(tensor, name, (torch.int32,), 1)
@@ -897,7 +899,7 @@ def delta_rule(qkv: torch.Tensor, offsets, beta: torch.Tensor, step: torch.Tenso
     _call("mxb_delta_rule", qkv.data_ptr(), qkv.stride(0), q_off, k_off, v_off, beta.data_ptr(), beta.stride(0), 0,
           step.data_ptr(), step.stride(0), step_bias.data_ptr(), rate.data_ptr(), state.data_ptr(), state.stride(0),
           state.shape[0], row_start.data_ptr(), row_length.data_ptr(), request_slots.data_ptr(), out.data_ptr(), rows,
-          heads, groups, dim, vdim, _CODES[qkv.dtype], status_word(qkv.device).data_ptr(), _stream())
+          heads, groups, dim, vdim, _CODES[qkv.dtype], int(longest), status_word(qkv.device).data_ptr(), _stream())
     return out
 
 

@@ -224,8 +224,8 @@ class ChannelDelta:
         S <- g S;  u = beta (v - S^T kn);  S <- S + kn u^T;  o = S^T qn                per head
 
     Each head's o over its root mean square times a weight over V (shared by
-    the heads) times sigmoid((a Wg1^T) Wg2^T), then Wo. S (float32
-    ``[H, D, V]``) and the convolution's last inputs are kept per request in
+    the heads) times sigmoid((a Wg1^T) Wg2^T), then Wo. S (float32, kept
+    transposed as ``[H, V, D]``) and the convolution's last inputs are kept per request in
     the cache's state slots. One product gives q, k, v, both low-rank inputs
     and the write strength's pre-activation; the step size's second product
     leaves in float32; unit norms, softplus, decay, sigmoid, the recurrence and
@@ -287,7 +287,7 @@ class ChannelDelta:
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed(kind="several", members=(
-            CacheNeed(kind="state", state_shape=(self.heads, self.dim, self.vdim), state_dtype="float32"),
+            CacheNeed(kind="state", state_shape=(self.heads, self.vdim, self.dim), state_dtype="float32"),
             self.conv.cache_need()))
 
     def parts(self):
@@ -304,7 +304,7 @@ class ChannelDelta:
                                     out_dtype=torch.float32)
         mixed = ops.delta_rule(qkv, (0, G * D, 2 * G * D), proj[:, at["beta_proj"]:at["beta_proj"] + H], step,
                                self.step_bias, self.rate, cache.members[0].state, rows["row_start"],
-                               rows["row_length"], ctx.request_slots, H, G, D, V)
+                               rows["row_length"], ctx.request_slots, H, G, D, V, longest=rows.get("longest", 0))
         gate = self.gate_up.forward(proj[:, at["gate_down_proj"]:at["gate_down_proj"] + self.gate_rank])
         return self.o.forward(ops.head_norm_gate(mixed, self.norm_weight, gate, H, self.eps, self.dtype))
 

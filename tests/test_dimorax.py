@@ -309,9 +309,9 @@ def test_cache_needs_and_the_shared_entry():
     needs = model.cache_needs()
     flat = [None if need is None else [(n.kind, tuple(n.state_shape) if n.kind == "state" else (n.kv_heads, n.head_dim, n.window))
                                        for n in need.flat()] for need in needs]
-    assert flat[0] == [("state", (4, 12, 20)), ("state", (2, 2 * 2 * 12 + 4 * 20))]
+    assert flat[0] == [("state", (4, 20, 12)), ("state", (2, 2 * 2 * 12 + 4 * 20))]
     assert flat[1] == [("kv_pages", (2, 24, None))] and flat[2] == [("kv_pages", (3, 64, 7))]
-    assert flat[3] is None and flat[4] == [("state", (2, 40, 8)), ("state", (1, 2 * 2 * 40 + 2 * 8))]
+    assert flat[3] is None and flat[4] == [("state", (2, 8, 40)), ("state", (1, 2 * 2 * 40 + 2 * 8))]
     assert not model.blocks[3].mixer.own_keys and model.blocks[3].mixer.qkv.out_features == 4 * 16
 
 
@@ -430,7 +430,7 @@ def test_delta_rule_kernel(dtype, heads, groups, dim, vdim):
                     "v": rounded(rng.normal(size=(total, heads * vdim)) * first, dtype),
                     "b": rounded(rng.normal(size=(total, heads)) * 2.0, dtype),
                     "s": rounded(rng.normal(size=(total, heads * dim)), torch.float32)})
-    state = torch.full((5, heads, dim, vdim), 3.0, device="cuda")
+    state = torch.full((5, heads, vdim, dim), 3.0, device="cuda")      # S transposed: a column's channels side by side
     for slot in slots:
         state[slot].zero_()
     got = [[] for _ in totals]
@@ -461,7 +461,7 @@ def test_delta_rule_kernel(dtype, heads, groups, dim, vdim):
                                           plain.sigmoid(s["b"][:, head]), decay[:, head])
             have = np.concatenate(got[row])[:, head * vdim:(head + 1) * vdim]
             assert np.abs(have - want).max() < 2e-4 * max(1.0, np.abs(want).max()), (row, head)
-            assert np.abs(state[slots[row], head].double().cpu().numpy() - last).max() < 2e-4 * max(1.0, np.abs(last).max())
+            assert np.abs(state[slots[row], head].double().cpu().numpy().T - last).max() < 2e-4 * max(1.0, np.abs(last).max())
             if total > 30:       # without the first token's write the last output is another
                 again, _ = plain.delta_rule(q[1:, group], k[1:, group], s["v"][1:, head * vdim:(head + 1) * vdim],
                                             plain.sigmoid(s["b"][1:, head]), decay[1:, head])
